@@ -10,12 +10,13 @@ namespace illm {
 
 // ---- requests
 
-CacheRequest CacheRequest::paged(int n_kv_heads, int head_dim, int window) {
+CacheRequest CacheRequest::paged(int n_kv_heads, int head_dim, int window, int v_head_dim) {
     CacheRequest r;
     r.kind = PagedKV;
     r.n_kv_heads = n_kv_heads;
     r.head_dim = head_dim;
     r.window = window;
+    r.v_head_dim = v_head_dim > 0 ? v_head_dim : head_dim;
     return r;
 }
 CacheRequest CacheRequest::state(std::vector<long long> shape, DType dtype) {
@@ -26,7 +27,8 @@ CacheRequest CacheRequest::state(std::vector<long long> shape, DType dtype) {
     return r;
 }
 bool CacheRequest::operator==(const CacheRequest& o) const {
-    return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && window == o.window && shape == o.shape &&
+    return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && v_head_dim == o.v_head_dim && window == o.window &&
+           shape == o.shape &&
            (kind != FixedState || dtype == o.dtype);
 }
 Json CacheRequest::to_json() const {
@@ -36,6 +38,7 @@ Json CacheRequest::to_json() const {
         j.set("kind", "kv");
         j.set("n_kv_heads", n_kv_heads);
         j.set("head_dim", head_dim);
+        if (v_head_dim != head_dim) j.set("v_head_dim", v_head_dim);
         j.set("window", window ? Json(window) : Json());
     } else {
         j.set("kind", "state");
@@ -51,7 +54,8 @@ CacheRequest CacheRequest::from_json(const Json& j) {
     const std::string kind = j.at("kind").is_string() ? j.at("kind").as_string() : "";
     if (kind == "kv")
         return paged((int)j.at("n_kv_heads").as_int(), (int)j.at("head_dim").as_int(),
-                     j.at("window").is_int() ? (int)j.at("window").as_int() : 0);
+                     j.at("window").is_int() ? (int)j.at("window").as_int() : 0,
+                     j.has("v_head_dim") && j.at("v_head_dim").is_int() ? (int)j.at("v_head_dim").as_int() : 0);
     if (kind == "state") {
         std::vector<long long> shape;
         for (const Json& d : j.at("shape").items()) shape.push_back(d.as_int());
@@ -177,7 +181,8 @@ void PageLedger::check() const {
 size_t SequenceCache::bytes_per_token(const std::map<int, CacheRequest>& requests, DType dtype) {
     size_t n = 0;
     for (auto& r : requests)
-        if (r.second.kind == CacheRequest::PagedKV) n += 2 * (size_t)r.second.n_kv_heads * r.second.head_dim * dtype_size(dtype);
+        if (r.second.kind == CacheRequest::PagedKV)
+            n += (size_t)r.second.n_kv_heads * (r.second.head_dim + r.second.v_head_dim) * dtype_size(dtype);
     return n;
 }
 
@@ -221,6 +226,8 @@ SequenceCache::SequenceCache(const std::map<int, CacheRequest>& requests, int nu
     for (PagedGroup& g : paged) {
         g.page_bytes = (size_t)g.request.n_kv_heads * page_size * g.request.head_dim * dtype_size(dtype);
         g.entry_bytes = g.page_bytes * num_pages;
+        g.v_page_bytes = (size_t)g.request.n_kv_heads * page_size * g.request.v_head_dim * dtype_size(dtype);
+        g.v_entry_bytes = g.v_page_bytes * num_pages;
     }
     for (StateGroup& g : states) g.entry_bytes = (size_t)num_slots * g.request.elements() * dtype_size(g.request.dtype);
     if (!device_) return;
@@ -234,10 +241,10 @@ SequenceCache::SequenceCache(const std::map<int, CacheRequest>& requests, int nu
     }
     for (PagedGroup& g : paged) {
         g.k = device_->alloc_persistent(g.entry_bytes * g.entries.size(), "the cache's keys", !poison);
-        g.v = device_->alloc_persistent(g.entry_bytes * g.entries.size(), "the cache's values", !poison);
+        g.v = device_->alloc_persistent(g.v_entry_bytes * g.entries.size(), "the cache's values", !poison);
         if (poison) {
             check_cuda(cudaMemsetAsync(g.k, 0xFF, g.entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
-            check_cuda(cudaMemsetAsync(g.v, 0xFF, g.entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
+            check_cuda(cudaMemsetAsync(g.v, 0xFF, g.v_entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
         }
     }
     for (StateGroup& g : states) g.state = device_->alloc_persistent(g.entry_bytes * g.entries.size(), "the per-sequence state", true);
@@ -267,9 +274,18 @@ void SequenceCache::poison_pages(PagedGroup& g, const std::vector<int>& pages) {
     std::copy(pages.begin(), pages.end(), poison_host_);
     check_cuda(cudaMemcpyAsync(poison_list_, poison_host_, pages.size() * 4, cudaMemcpyHostToDevice, device_->stream()),
                "uploading the pages to poison");
-    check_kernel(illm_poison_pages(g.k, g.v, (long long)g.entry_bytes, (int)g.entries.size(), (long long)g.page_bytes, poison_list_,
-                                   (int)pages.size(), device_->stream()),
-                 "poison_pages");
+    if (g.v_page_bytes == g.page_bytes) {
+        check_kernel(illm_poison_pages(g.k, g.v, (long long)g.entry_bytes, (int)g.entries.size(), (long long)g.page_bytes, poison_list_,
+                                       (int)pages.size(), device_->stream()),
+                     "poison_pages");
+    } else {            // keys and values have rows of different sizes: one launch each
+        check_kernel(illm_poison_pages(g.k, g.k, (long long)g.entry_bytes, (int)g.entries.size(), (long long)g.page_bytes, poison_list_,
+                                       (int)pages.size(), device_->stream()),
+                     "poison_pages");
+        check_kernel(illm_poison_pages(g.v, g.v, (long long)g.v_entry_bytes, (int)g.entries.size(), (long long)g.v_page_bytes, poison_list_,
+                                       (int)pages.size(), device_->stream()),
+                     "poison_pages");
+    }
 }
 
 int SequenceCache::alloc_slot() {
@@ -371,7 +387,7 @@ KVView SequenceCache::kv_view(int entry, const int* table_dev) const {
     const PagedGroup& g = paged[it->second.group];
     KVView v;
     v.k = g.k ? (char*)g.k + (size_t)it->second.index * g.entry_bytes : nullptr;
-    v.v = g.v ? (char*)g.v + (size_t)it->second.index * g.entry_bytes : nullptr;
+    v.v = g.v ? (char*)g.v + (size_t)it->second.index * g.v_entry_bytes : nullptr;
     v.block_table = table_dev;
     v.width = width;
     v.num_pages = num_pages;
@@ -379,6 +395,7 @@ KVView SequenceCache::kv_view(int entry, const int* table_dev) const {
     v.window = g.request.window;
     v.n_kv_heads = g.request.n_kv_heads;
     v.head_dim = g.request.head_dim;
+    v.v_head_dim = g.request.v_head_dim;
     v.dtype = dtype_;
     return v;
 }
@@ -404,7 +421,7 @@ std::vector<int> SequenceCache::pages_free() const {
 }
 size_t SequenceCache::storage_bytes() const {
     size_t n = 0;
-    for (const PagedGroup& g : paged) n += 2 * g.entry_bytes * g.entries.size();
+    for (const PagedGroup& g : paged) n += (g.entry_bytes + g.v_entry_bytes) * g.entries.size();
     return n;
 }
 

@@ -5,8 +5,8 @@
 // window) or FixedState(shape, dtype).  Cache entries (one per writing entry of the model's
 // schedule) with equal requests form a group; every group has storage, a page pool and page tables
 // of its own, so groups with different needs (all keys, a window of them, another head size) live
-// side by side.  Device storage of a paged group: k, v : [entries, pages, kv heads, page_size,
-// head_dim] in the engine's dtype; of a state group: [entries, slots, elements].
+// side by side.  Device storage of a paged group: k : [entries, pages, kv heads, page_size,
+// head_dim], v likewise with its own row size, in the engine's dtype; of a state group: [entries, slots, elements].
 //
 // Life of a sequence: alloc_slot() (state zeroed) -> plan_step() / commit_step() once per step
 // (pages are reserved before the step runs and the length advances after it; abandon_step() gives
@@ -35,12 +35,13 @@ namespace illm {
 struct CacheRequest {
     enum Kind { None, PagedKV, FixedState } kind = None;
     // PagedKV: keys and values of every position (window 0) or of the last `window` positions
-    int n_kv_heads = 0, head_dim = 0, window = 0;
+    // (value rows of v_head_dim elements; equal to head_dim unless the mixer says otherwise)
+    int n_kv_heads = 0, head_dim = 0, window = 0, v_head_dim = 0;
     // FixedState: `elements` values of `dtype` per sequence, zeroed when a slot is handed out
     std::vector<long long> shape;
     DType dtype = DType::F32;
 
-    static CacheRequest paged(int n_kv_heads, int head_dim, int window = 0);
+    static CacheRequest paged(int n_kv_heads, int head_dim, int window = 0, int v_head_dim = 0);
     static CacheRequest state(std::vector<long long> shape, DType dtype = DType::F32);
     long long elements() const { long long n = 1; for (long long s : shape) n *= s; return n; }
     bool operator==(const CacheRequest& o) const;
@@ -98,6 +99,7 @@ struct KVView {
     void* v = nullptr;
     const int* block_table = nullptr;   // int32 [B, width] on the device, rows in the order of the step's sequences
     int width = 0, num_pages = 0, page_size = 0, window = 0, n_kv_heads = 0, head_dim = 0;
+    int v_head_dim = 0;         // v: [pages, kv heads, page_size, v_head_dim]
     DType dtype = DType::BF16;
     bool writes = true;
 };
@@ -132,7 +134,8 @@ public:
         std::vector<int> entries;
         std::unique_ptr<PageLedger> ledger;
         void *k = nullptr, *v = nullptr;
-        size_t entry_bytes = 0, page_bytes = 0;
+        size_t entry_bytes = 0, page_bytes = 0;          // of the keys
+        size_t v_entry_bytes = 0, v_page_bytes = 0;      // of the values
     };
     struct StateGroup {
         CacheRequest request;

@@ -203,13 +203,15 @@ Registry& registry() {
 }
 }  // namespace
 
-void register_llama_architecture();   // config/llama.cpp
+void register_llama_architecture();     // config/llama.cpp
+void register_vokelix_architecture();   // config/vokelix.cpp
 
 static void ensure_builtin() {
     static bool done = false;
     if (!done) {
         done = true;
         register_llama_architecture();
+        register_vokelix_architecture();
     }
 }
 
@@ -247,10 +249,17 @@ std::unique_ptr<ArchConfig> config_from_json(const Json& d, const std::string& m
     if (!d.is_object()) throw ConfigError("config.json: expected a JSON object");
     std::string name = model_name;
     if (name.empty()) {
-        const Json& archs = d.at("architectures");
-        if (!archs.is_array() || archs.size() == 0 || !archs[0].is_string())
+        // the model class: architectures[0], or a single name under 'architecture'
+        if (d.has("architectures")) {
+            const Json& archs = d.at("architectures");
+            if (!archs.is_array() || archs.size() == 0 || !archs[0].is_string())
+                throw ConfigError("config.json: required key 'architectures' (a list with the model class name) is missing");
+            name = archs[0].as_string();
+        } else if (d.has("architecture") && d.at("architecture").is_string()) {
+            name = d.at("architecture").as_string();
+        } else {
             throw ConfigError("config.json: required key 'architectures' (a list with the model class name) is missing");
-        name = archs[0].as_string();
+        }
     }
     return registry().archs.at(resolve_architecture(name))(d);
 }

@@ -14,6 +14,11 @@
 // and sum, and are merged in a fixed order.  The split of the keys depends only on the
 // token's own position and window, so its result does not depend on the step it is part of.
 //   score = (q . k) * scale;  keys lo..p with lo = max(0, p - window + 1) (window 0 = all)
+//
+// Three options for mixers that are more than the plain softmax attention: values of another head
+// size than the keys (dv); a sink, one learned number per head whose exponential joins the
+// softmax denominator as one more term without a value (sinks[h], not scaled); and an output gate,
+// sigmoid(gate[t * gate_stride + h]) multiplied into the head's output.
 #include <math.h>
 
 #include "common.cuh"
@@ -27,11 +32,12 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
                          const TA* __restrict__ vc, const int* __restrict__ block_table,
                          int max_pages, const int* __restrict__ token_pos,
                          const int* __restrict__ token_seq, TA* __restrict__ out, int nh, int nkv,
-                         int d, int page_size, int window, float scale) {
+                         int d, int page_size, int window, float scale, int dv,
+                         const float* __restrict__ sinks, const float* __restrict__ gate, int gate_stride) {
     pdl_grid_sync();
     extern __shared__ float smem[];
     float* qs = smem;                 // [d]
-    float* acc_s = smem + d;          // [AG_WARPS][d]
+    float* acc_s = smem + d;          // [AG_WARPS][dv]
     __shared__ float m_s[AG_WARPS], l_s[AG_WARPS];
 
     const int t = blockIdx.x, h = blockIdx.y;
@@ -50,6 +56,7 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
 #pragma unroll
     for (int i = 0; i < AG_MAX_D / 32; i++) acc[i] = 0.f;
 
+    const bool vec = (d & 7) == 0;
     for (int kb = lo + warp * 32; kb <= p; kb += AG_WARPS * 32) {
         const int key = kb + lane;
         const bool valid = key <= p;
@@ -57,15 +64,19 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
         long long off = 0;
         if (valid) {
             const int page = bt[key / page_size];
-            off = (((long long)page * nkv + hk) * page_size + (key % page_size)) * d;
-            const TA* kr = kc + off;
+            off = ((long long)page * nkv + hk) * page_size + (key % page_size);      // in rows
+            const TA* kr = kc + off * d;
             float dot = 0.f;
+            if (vec) {
 #pragma unroll 4
-            for (int c = 0; c < d; c += 8) {
-                float f[8];
-                load8(kr + c, f);
+                for (int c = 0; c < d; c += 8) {
+                    float f[8];
+                    load8(kr + c, f);
 #pragma unroll
-                for (int i = 0; i < 8; i++) dot = fmaf(qs[c + i], f[i], dot);
+                    for (int i = 0; i < 8; i++) dot = fmaf(qs[c + i], f[i], dot);
+                }
+            } else {
+                for (int c = 0; c < d; c++) dot = fmaf(qs[c], to_f32(kr[c]), dot);
             }
             s = dot * scale;
         }
@@ -80,11 +91,11 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
         for (int j = 0; j < nk; j++) {
             const float pj = __shfl_sync(0xffffffffu, pe, j);
             const long long oj = __shfl_sync(0xffffffffu, off, j);
-            const TA* vr = vc + oj;
+            const TA* vr = vc + oj * dv;
 #pragma unroll
             for (int i = 0; i < AG_MAX_D / 32; i++) {
                 const int c = lane + 32 * i;
-                if (c < d) acc[i] = fmaf(pj, to_f32(vr[c]), acc[i]);
+                if (c < dv) acc[i] = fmaf(pj, to_f32(vr[c]), acc[i]);
             }
         }
         m = m_new;
@@ -97,24 +108,30 @@ attention_generic_kernel(const TA* __restrict__ q, int q_stride, const TA* __res
 #pragma unroll
     for (int i = 0; i < AG_MAX_D / 32; i++) {
         const int c = lane + 32 * i;
-        if (c < d) acc_s[warp * d + c] = acc[i];
+        if (c < dv) acc_s[warp * dv + c] = acc[i];
     }
     __syncthreads();
     float M = m_s[0];
 #pragma unroll
     for (int w = 1; w < AG_WARPS; w++) M = fmaxf(M, m_s[w]);
     float wgt[AG_WARPS], den = 0.f;
+    if (sinks) {
+        const float sk = sinks[h];
+        M = fmaxf(M, sk);
+        den = expf(sk - M);
+    }
 #pragma unroll
     for (int w = 0; w < AG_WARPS; w++) {
         wgt[w] = (m_s[w] == -INFINITY) ? 0.f : expf(m_s[w] - M);
         den += l_s[w] * wgt[w];
     }
-    const float inv = 1.0f / den;
-    TA* o = out + ((size_t)t * nh + h) * d;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float inv = 1.0f / den;
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + h]));
+    TA* o = out + ((size_t)t * nh + h) * dv;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float num = 0.f;
 #pragma unroll
-        for (int w = 0; w < AG_WARPS; w++) num += acc_s[w * d + c] * wgt[w];
+        for (int w = 0; w < AG_WARPS; w++) num += acc_s[w * dv + c] * wgt[w];
         o[c] = from_f32<TA>(num * inv);
     }
 }
@@ -123,20 +140,22 @@ extern "C" int illm_attention_generic(const void* q, int q_stride, const void* k
                                       const int* block_table, int max_pages, const int* token_pos,
                                       const int* token_seq, void* out, int act_dtype, int T, int nh,
                                       int nkv, int d, int page_size, int window, float scale,
+                                      int dv, const float* sinks, const float* gate, int gate_stride,
                                       void* stream) {
     if (T <= 0) return 0;
-    if (d <= 0 || d > AG_MAX_D || (d & 7) || nkv <= 0 || nh % nkv || nh > 65535) return ILLM_ERR_BAD_ARG;
+    if (dv <= 0) dv = d;
+    if (d <= 0 || d > AG_MAX_D || dv > AG_MAX_D || nkv <= 0 || nh % nkv || nh > 65535) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
-    size_t smem = (size_t)(1 + AG_WARPS) * d * sizeof(float);
+    size_t smem = ((size_t)d + (size_t)AG_WARPS * dv) * sizeof(float);
     if (act_dtype == ILLM_BF16)
         illm_launch(attention_generic_kernel<bf16>, dim3(grid), dim3(AG_WARPS * 32), smem, s, 
             (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages,
-            token_pos, token_seq, (bf16*)out, nh, nkv, d, page_size, window, scale);
+            token_pos, token_seq, (bf16*)out, nh, nkv, d, page_size, window, scale, dv, sinks, gate, gate_stride);
     else if (act_dtype == ILLM_F32)
         illm_launch(attention_generic_kernel<float>, dim3(grid), dim3(AG_WARPS * 32), smem, s, 
             (const float*)q, q_stride, (const float*)kc, (const float*)vc, block_table, max_pages,
-            token_pos, token_seq, (float*)out, nh, nkv, d, page_size, window, scale);
+            token_pos, token_seq, (float*)out, nh, nkv, d, page_size, window, scale, dv, sinks, gate, gate_stride);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();

@@ -22,13 +22,18 @@ int illm_attention_decode_ring(const void* q, int q_stride, const void* kc, cons
 int illm_attention_decode_ring_rope(const void* qkv, const float* partials, int splits, long long split_stride, const float* cos_sin, int rot, int table_positions, int write_kv, void* kc, void* vc, long long n_pages, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_splits, int* err, int* step_err, void* stream);
 
 // attention_generic.cu
-int illm_attention_generic(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int page_size, int window, float scale, void* stream);
+int illm_attention_generic(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int nh, int nkv, int d, int page_size, int window, float scale, int dv, const float* sinks, const float* gate, int gate_stride, void* stream);
 
 // attention_prefill.cu
 int illm_attention_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, void* stream);
 
 // attention_prefill_tc.cu
 int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, int* err, void* stream);
+
+// decay_state.cu
+long long illm_decay_scan_smem(int d, int dv);
+int illm_decay_scan(const float* x, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, void* stream);
+int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
 
 // embedding.cu
 int illm_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H, int V, int* err, void* stream);
@@ -46,6 +51,12 @@ int illm_splitk_reduce(const float* ws, void* out, int out_dtype, long long n, i
 
 // gemm_tc2.cu
 int illm_gemm_bf16_tc2(const void* X, const void* W, void* out, int out_dtype, int epi, int M, int N, int K, int* err, void* stream);
+
+// postnorm.cu
+int illm_scale_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* w, void* y, int y_dtype, int n_rows, int H, float alpha, float eps, void* stream);
+
+// qk_prep.cu
+int illm_qk_prep(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq, const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, void* stream);
 
 // rmsnorm.cu
 int illm_add_rmsnorm(float* resid, const void* delta, const void* w, int w_dtype, void* y, int act_dtype, const int* rows, int n_rows, int H, float eps, int write_resid, void* stream);

@@ -375,19 +375,86 @@ Mat rope_kv_write(Device& dev, const MatOrPartials& in, const float* cos_sin, in
     return qkv;
 }
 
-Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale) {
-    if (g.head_dim % 8 || g.head_dim > kMaxHeadDimGeneric)
-        throw KernelError("attention: head size " + std::to_string(g.head_dim) + " is not supported (multiples of 8 up to " +
-                          std::to_string(kMaxHeadDimGeneric) + ")");
+Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
+                      const AttentionExtras* extras) {
+    const int dv = kv.v_head_dim > 0 ? kv.v_head_dim : g.head_dim;
+    if (g.head_dim <= 0 || g.head_dim > kMaxHeadDimGeneric || dv > kMaxHeadDimGeneric)
+        throw KernelError("attention: head size " + std::to_string(g.head_dim) + " (values " + std::to_string(dv) +
+                          ") is not supported (up to " + std::to_string(kMaxHeadDimGeneric) + ")");
     if (g.n_kv_heads <= 0 || g.n_heads % g.n_kv_heads) throw KernelError("attention: heads must be a multiple of kv heads");
     need(qkv, "qkv");
     check_cache(kv, qkv.dtype, g, "attention_generic");
-    Mat out = new_mat(dev, qkv.rows, (long long)g.n_heads * g.head_dim, qkv.dtype);
+    Mat out = new_mat(dev, qkv.rows, (long long)g.n_heads * dv, qkv.dtype);
     check_kernel(illm_attention_generic(qkv.p, (int)qkv.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p,
                                         code_of(qkv.dtype, "attention_generic"), (int)qkv.rows, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size,
-                                        kv.window, scale, dev.stream()),
+                                        kv.window, scale, dv, extras ? extras->sinks : nullptr, extras ? extras->gate : nullptr,
+                                        extras ? extras->gate_stride : 0, dev.stream()),
                  "attention_generic");
     return out;
+}
+
+// ---- pieces of mixers other than the plain attention
+
+Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const Mat* delta, const Mat& w, float alpha, float eps, DType out_dtype) {
+    need(resid, "resid", true, DType::F32);
+    need(w, "norm weight", true, DType::F32);
+    const long long H = resid.cols;
+    if (w.rows * w.cols != H)
+        throw KernelError("norm weight has " + std::to_string(w.rows * w.cols) + " elements, the rows have " + std::to_string(H));
+    if (delta) {
+        need(*delta, "delta");
+        if (delta->rows != resid.rows || delta->cols != H) throw KernelError("scale_add_rmsnorm: delta does not match the stream");
+    }
+    Mat y = new_mat(dev, resid.rows, H, out_dtype);
+    check_kernel(illm_scale_add_rmsnorm((float*)resid.p, delta ? delta->p : nullptr, delta ? code_of(delta->dtype, "scale_add_rmsnorm") : 0,
+                                        (const float*)w.p, y.p, code_of(out_dtype, "scale_add_rmsnorm"), (int)resid.rows, (int)H, alpha, eps,
+                                        dev.stream()),
+                 "scale_add_rmsnorm");
+    return y;
+}
+
+Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepView& ctx, const KVView& kv, DType act_dtype) {
+    need(x, "the packed projection");
+    if (x.dtype != DType::F32 && x.dtype != act_dtype) throw KernelError("qk_prep: the projection must be float32 or the activation dtype");
+    const bool has_kv = p.k_off >= 0;
+    const int dv = kv.v_head_dim > 0 ? kv.v_head_dim : g.head_dim;
+    const bool store = has_kv && kv.writes;
+    if (store) check_cache(kv, act_dtype, g, "qk_prep");
+    if (p.rot_dim && !p.cos_sin) throw KernelError("qk_prep: a rotation needs its cos/sin table");
+    Mat q = new_mat(dev, x.rows, (long long)g.n_heads * g.head_dim, act_dtype);
+    check_kernel(illm_qk_prep(x.p, code_of(x.dtype, "qk_prep"), (int)x.cols, p.q_off, has_kv ? p.k_off : -1, p.v_off, g.n_heads, g.n_kv_heads, g.head_dim, dv,
+                              p.q_bias, p.k_bias, p.v_bias, p.q_norm, p.k_norm, p.eps, p.cos_sin, p.rot_dim, p.pairs ? 1 : 0, (int)p.n_pos,
+                              ctx.token_pos, ctx.token_seq, kv.block_table, kv.width, kv.page_size, q.p, store ? kv.k : nullptr,
+                              store ? kv.v : nullptr, code_of(act_dtype, "qk_prep"), (int)x.rows, ctx.err, dev.stream()),
+                 "qk_prep");
+    return q;
+}
+
+bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }
+
+Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ctx, const StateView& st) {
+    need(x, "the packed projection", true, DType::F32);
+    if (!st.state || st.dtype != DType::F32 || st.elements != (long long)p.n_heads * p.head_dim * p.v_head_dim)
+        throw KernelError("decay_scan: the cache entry does not hold float32 state of heads x head size x value size");
+    if (!decay_scan_supported(p.head_dim, p.v_head_dim))
+        throw KernelError("decay_scan: a state of " + std::to_string(p.head_dim) + " x " + std::to_string(p.v_head_dim) +
+                          " per head does not fit a block's shared memory");
+    Mat out = new_mat_exact(dev, x.rows, (long long)p.n_heads * p.v_head_dim, DType::F32);
+    check_kernel(illm_decay_scan((const float*)x.p, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.head_dim, p.v_head_dim, p.qk_act, p.v_act,
+                                 p.rot_dim ? p.cos_sin : nullptr, p.rot_dim, (int)p.n_pos, p.k_scale, p.decay, (float*)st.state, st.slots, ctx.cu_q,
+                                 ctx.token_pos, (float*)out.p, ctx.B, ctx.err, dev.stream()),
+                 "decay_scan");
+    return out;
+}
+
+Mat group_norm_gate(Device& dev, const Mat& o, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
+                    DType out_dtype) {
+    need(o, "the recurrence's output", true, DType::F32);
+    Mat y = new_mat(dev, o.rows, o.cols, out_dtype);
+    check_kernel(illm_group_norm_gate((const float*)o.p, (int)o.rows, (int)o.cols, group, w, eps, gate, gate_ld, gate_act, y.p,
+                                      code_of(out_dtype, "group_norm_gate"), dev.stream()),
+                 "group_norm_gate");
+    return y;
 }
 
 typedef int (*DecodeFn)(const void*, int, const void*, const void*, const int*, int, const int*, const int*, float*, float*, void*, int, int,
@@ -545,6 +612,13 @@ void convert(Device& dev, const void* src, DType src_dtype, void* dst, DType dst
     if (rc == 10001)
         throw KernelError(std::string("a tensor stored as ") + dtype_word(src_dtype) + " cannot be brought to " + dtype_word(dst_dtype));
     check_kernel(rc, "convert");
+}
+
+Mat cast(Device& dev, const Mat& x, DType dtype) {
+    if (x.dtype == dtype) return x;
+    Mat y = new_mat(dev, x.rows, x.cols, dtype);
+    convert(dev, x.p, x.dtype, y.p, dtype, x.rows * x.cols);
+    return y;
 }
 
 }  // namespace ops

@@ -141,7 +141,16 @@ struct Geometry { int n_heads, n_kv_heads, head_dim; };
 // as unreduced slices, a new one (the slices are added up on the way).
 Mat rope_kv_write(Device& dev, const MatOrPartials& qkv, const float* cos_sin, int rot_dim, long long n_pos, const StepView& ctx,
                   const KVView& kv, Geometry g);
-Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
+// Options of the generic attention kernel beyond the plain softmax attention: a per-head sink in the
+// softmax denominator (float32 [n_heads]), and a per-head output gate, sigmoid(gate[t * gate_stride + h])
+// (float32).  The value head size is the cache entry's (KVView::v_head_dim).
+struct AttentionExtras {
+    const float* sinks = nullptr;
+    const float* gate = nullptr;
+    int gate_stride = 0;
+};
+Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
+                      const AttentionExtras* extras = nullptr);
 Mat attention_decode(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale, long long max_len);
 Mat attention_decode_gqa(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale, long long max_len);
 struct FusedRope { const float* cos_sin; int rot_dim; long long n_pos; bool write_kv; int* step_err; };
@@ -152,6 +161,47 @@ Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const St
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
 
+// ---- pieces of mixers other than the plain attention
+
+// stream.x <- rmsnorm(alpha * stream.x + delta) * w (w float32, the stream float32); returns the new rows
+// in `out_dtype` as well (what the next sublayer reads).
+Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const Mat* delta, const Mat& weight_f32, float alpha, float eps, DType out_dtype);
+
+// Between the packed projection x [T, ld] (float32 or the activation dtype) of an attention layer and its attention kernel:
+// optional biases, optional RMS norms over a token's whole q and whole k projection, rotation of the
+// first `rot_dim` channels of every head (interleaved pairs or rotate-half) from a (cos, sin) table,
+// q to a new [T, n_heads * head_dim] matrix of `act_dtype`, k and v into the pages.  k_off < 0: q only.
+struct QkPrep {
+    int q_off = 0, k_off = -1, v_off = -1;
+    const float *q_bias = nullptr, *k_bias = nullptr, *v_bias = nullptr;
+    const float *q_norm = nullptr, *k_norm = nullptr;
+    float eps = 0.f;
+    const float* cos_sin = nullptr;
+    int rot_dim = 0;
+    bool pairs = false;
+    long long n_pos = 0;
+};
+Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepView& ctx, const KVView& kv, DType act_dtype);
+
+// The decayed linear-attention recurrence over per-sequence state (csrc/decay_state.cu): x_f32 is the
+// packed float32 projection, state the cache entry's [slots, heads, d, dv] float32.  Returns float32
+// [T, heads * dv].
+struct DecayScan {
+    int q_off = 0, k_off = 0, v_off = 0;
+    int n_heads = 0, head_dim = 0, v_head_dim = 0;
+    int qk_act = 0, v_act = 0;          // 0: none, 1: silu
+    const float* cos_sin = nullptr;     // rotate-half table or nullptr
+    int rot_dim = 0;
+    long long n_pos = 0;
+    float k_scale = 1.f;
+    const float* decay = nullptr;       // float32 [heads] on the device
+};
+Mat decay_scan(Device& dev, const Mat& x_f32, const DecayScan& p, const StepView& ctx, const StateView& st);
+bool decay_scan_supported(int head_dim, int v_head_dim);
+// y = o / sqrt(mean over groups of `group` columns (o^2) + eps) (* w) * act(gate), gate_act 1: silu, 2: sigmoid
+Mat group_norm_gate(Device& dev, const Mat& o_f32, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
+                    DType out_dtype);
+
 // float32 [B, V] -> int32 [B], the lowest id among equal maxima.
 int* argmax(Device& dev, const float* logits, long long B, long long V, int* out /* nullptr: from the arena */);
 // Temperature / repetition penalty / top-k / top-p sampling, one draw per row (the reference's chain,
@@ -160,6 +210,8 @@ int* sample(Device& dev, const float* logits, long long B, long long V, const fl
             float repeat_penalty, const int* last_tokens, int n_last, int* out /* nullptr: from the arena */);
 void fill_random(Device& dev, void* out, DType dtype, long long n, unsigned long long key, float std, float mean);
 void convert(Device& dev, const void* src, DType src_dtype, void* dst, DType dst_dtype, long long n);
+// x in another dtype, as a new activation (x itself if it has that dtype already)
+Mat cast(Device& dev, const Mat& x, DType dtype);
 
 long long launch_count();               // kernels of this package launched so far (graph replays counted by the engine)
 void count_replayed_launches(long long n);

@@ -43,7 +43,7 @@ _KERNEL_SIGNATURES = {
     "illm_residual_add": [P_, P_, I_, LL_, P_],
     "illm_swiglu": [P_, P_, I_, I_, I_, P_],
     "illm_rope_kv_write": [P_, P_, P_, P_, P_, I_, P_, P_, I_, I_, I_, I_, I_, I_, I_, I_, I_, P_, P_],
-    "illm_attention_generic": [P_, I_, P_, P_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_],
+    "illm_attention_generic": [P_, I_, P_, P_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, I_, P_, P_, I_, P_],
     "illm_attention_decode": [P_, I_, P_, P_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_, F_, I_, P_],
     "illm_attention_decode_supported": [I_, I_, I_],
     "illm_attention_decode_gqa": [P_, I_, P_, P_, P_, I_, P_, P_, P_, P_, P_, I_, I_, I_, I_, I_, I_, F_, I_, P_],
@@ -353,7 +353,8 @@ def attention_generic(qkv, k_cache, v_cache, block_table, token_pos, token_seq, 
     _check(load().illm_attention_generic(
         _ptr(qkv), qkv.shape[1], _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
         block_table.shape[1], _ptr(token_pos), _ptr(token_seq), _ptr(out), act_code(qkv.dtype), T,
-        n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _stream()),
+        n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), head_dim, None, None, 0,
+        _stream()),
         "attention_generic")
     return out
 

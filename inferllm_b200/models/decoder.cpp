@@ -17,7 +17,7 @@ DecoderModel::DecoderModel(const ModelSpec& s, Runtime* runtime) : spec(s), rt(r
         const BlockKind& kind = lookup_block(ls.block);
         Layer l;
         l.mixer = build_mixer(ls.mixer, rt);
-        l.ffn = build_feed_forward(ls.ffn, rt);
+        if (!ls.ffn.kind.empty()) l.ffn = build_feed_forward(ls.ffn, rt);      // a layer may have no feed-forward
         l.block = kind.make();
         l.block->mixer = l.mixer.get();
         l.block->ffn = l.ffn.get();
@@ -40,7 +40,7 @@ std::vector<std::pair<std::string, Part*>> DecoderModel::owners() const {
     for (size_t i = 0; i < layers_.size(); i++) {
         const LayerSpec& ls = spec.layers[i];
         out.emplace_back(ls.prefix + role_name(ls, "mixer"), layers_[i].mixer.get());
-        out.emplace_back(ls.prefix + role_name(ls, "ffn"), layers_[i].ffn.get());
+        if (layers_[i].ffn) out.emplace_back(ls.prefix + role_name(ls, "ffn"), layers_[i].ffn.get());
         for (auto& n : layers_[i].norms) out.emplace_back(ls.prefix + role_name(ls, n.first), n.second.get());
     }
     out.emplace_back(spec.final_norm.get_string("name", ""), final_norm_.get());
@@ -107,7 +107,7 @@ Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, co
 
 bool DecoderModel::graph_safe() const {
     for (const Layer& l : layers_)
-        if (!l.mixer->graph_safe() || !l.ffn->graph_safe()) return false;
+        if (!l.mixer->graph_safe() || (l.ffn && !l.ffn->graph_safe())) return false;
     return true;
 }
 bool DecoderModel::pad_safe() const {

@@ -4,6 +4,8 @@
 
 namespace illm {
 
+void register_decay_parts(std::map<std::string, PartFactory<Mixer>>& mixers);      // parts/decay_mixer.cpp
+
 // ---- registries
 
 namespace {
@@ -101,20 +103,52 @@ OwnedMat fetch_owned(Runtime* rt, TensorSource& src, const std::string& name, DT
     return o;
 }
 
+std::vector<double> rotary_frequencies(double theta, int rot_dim, const Json* scaling, double* magnitude) {
+    const int half = rot_dim / 2;
+    std::vector<double> f((size_t)half);
+    for (int j = 0; j < half; j++) f[j] = std::pow(theta, -2.0 * j / rot_dim);
+    *magnitude = 1.0;
+    if (!scaling || !scaling->is_object()) return f;
+    auto num = [&](const char* key) {
+        if (!scaling->has(key) || !scaling->at(key).is_number()) throw ConfigError(std::string("rotary scaling: '") + key + "' must be a number");
+        return scaling->at(key).as_double();
+    };
+    const double factor = num("factor"), original = num("original"), fast = num("fast"), slow = num("slow");
+    if (!(factor > 0) || !(original > 0) || !(fast > 0) || !(slow > 0)) throw ConfigError("rotary scaling: all four numbers must be positive");
+    // the (real-valued) pair index whose wave turns `turns` times within `original` positions
+    auto pair_of = [&](double turns) { return rot_dim * std::log(original / (2.0 * M_PI * turns)) / (2.0 * std::log(theta)); };
+    const double lo = std::max(std::floor(pair_of(fast)), 0.0), hi = std::min(std::ceil(pair_of(slow)), (double)rot_dim - 1.0);
+    for (int j = 0; j < half; j++) {
+        const double ramp = std::min(1.0, std::max(0.0, ((double)j - lo) / std::max(hi - lo, 0.001)));
+        f[j] = f[j] / factor * ramp + f[j] * (1.0 - ramp);
+    }
+    *magnitude = 0.1 * std::log(factor) + 1.0;
+    return f;
+}
+
 std::shared_ptr<PositionTable> shared_position_table(Runtime* rt, double theta, int rot_dim, long long positions) {
-    char key[96];
-    snprintf(key, sizeof key, "%.17g/%d/%lld", theta, rot_dim, positions);
+    double one;
+    return shared_position_table(rt, rotary_frequencies(theta, rot_dim, nullptr, &one), 1.0, positions);
+}
+
+std::shared_ptr<PositionTable> shared_position_table(Runtime* rt, const std::vector<double>& freqs, double magnitude, long long positions) {
+    std::string key = std::to_string(positions);
+    char word[40];
+    snprintf(word, sizeof word, "/%.17g", magnitude);
+    key += word;
+    for (double f : freqs) {
+        snprintf(word, sizeof word, "/%.17g", f);
+        key += word;
+    }
     auto it = rt->position_tables.find(key);
     if (it != rt->position_tables.end()) return it->second;
-    const int half = rot_dim / 2;
+    const int half = (int)freqs.size(), rot_dim = 2 * half;
     std::vector<float> host((size_t)positions * half * 2);
-    std::vector<double> inv((size_t)half);
-    for (int j = 0; j < half; j++) inv[j] = std::pow(theta, -2.0 * j / rot_dim);
     for (long long p = 0; p < positions; p++)
         for (int j = 0; j < half; j++) {
-            const double ang = (double)p * inv[j];
-            host[((size_t)p * half + j) * 2] = (float)std::cos(ang);
-            host[((size_t)p * half + j) * 2 + 1] = (float)std::sin(ang);
+            const double ang = (double)p * freqs[j];
+            host[((size_t)p * half + j) * 2] = (float)(std::cos(ang) * magnitude);
+            host[((size_t)p * half + j) * 2 + 1] = (float)(std::sin(ang) * magnitude);
         }
     auto t = std::make_shared<PositionTable>();
     t->positions = positions;
@@ -135,17 +169,48 @@ namespace {
 // (src/kern/naive/naive.cpp:186-207, weight multiply :138-149): y = x / sqrt(mean(x^2) + eps) * w.  The
 // reference fixes eps in code (1e-6 in the layers, src/graph/llama_like.cpp:77-78; 1e-5 in the head,
 // src/core/graph.h:160-163); here it is a parameter of the part.
+//
+// Three parameters beyond the reference's norm: `weight_offset` (a weight stored as w - offset, e.g.
+// around zero for offset 1; the offset is added once, in float32, when the weight is loaded),
+// `residual_scale` (the factor on the stream in the norm-after-the-sum arrangement, see
+// forward_into_stream) and `tensor` (the weight's name below the part's prefix, "weight" if not given).
 struct RMSNorm : Norm {
     long long size;
-    float eps;
+    float eps, weight_offset, residual_scale;
+    std::string tensor;
     OwnedMat weight;
-    RMSNorm(const PartSpec& s, Runtime* rt) : Norm(s, rt), size(s.get_int("size")), eps((float)s.get_double("eps")) {
+    RMSNorm(const PartSpec& s, Runtime* rt)
+            : Norm(s, rt), size(s.get_int("size")), eps((float)s.get_double("eps")), weight_offset((float)s.get_double("weight_offset", 0.0)),
+              residual_scale((float)s.get_double("residual_scale", 1.0)), tensor(s.get_string("tensor", "weight")) {
         if (size <= 0 || !(eps > 0)) throw ConfigError("rmsnorm: size and eps must be positive");
     }
-    TensorDecls tensors() const override { return {{"weight", TensorDecl{{size}, "norm"}}}; }
+    bool keeps_f32() const { return weight_offset != 0.f || spec.get_bool("float32_weight", false); }
+    TensorDecls tensors() const override { return {{tensor, TensorDecl{{size}, weight_offset == 1.f ? "matrix" : "norm"}}}; }
     void load(TensorSource& src) override {
-        // a weight stored in 32-bit stays 32-bit; bfloat16 stays bfloat16 (the kernel takes both)
-        weight = fetch_owned(rt, src, "weight", src.kept_dtype("weight"), "a norm weight");
+        if (!keeps_f32()) {
+            // a weight stored in 32-bit stays 32-bit; bfloat16 stays bfloat16 (the kernel takes both)
+            weight = fetch_owned(rt, src, tensor, src.kept_dtype(tensor), "a norm weight");
+            return;
+        }
+        weight = fetch_owned(rt, src, tensor, DType::F32, "a norm weight");
+        if (weight_offset != 0.f) {
+            std::vector<float> host((size_t)size);
+            rt->dev->synchronize();
+            check_cuda(cudaMemcpy(host.data(), weight.m.p, host.size() * sizeof(float), cudaMemcpyDeviceToHost), "reading a norm weight");
+            for (float& v : host) v = weight_offset + v;
+            check_cuda(cudaMemcpy(weight.m.p, host.data(), host.size() * sizeof(float), cudaMemcpyHostToDevice), "writing a norm weight");
+        }
+    }
+    Mat forward_into_stream(ResidualStream& stream) override {
+        if (weight.m.dtype != DType::F32) throw EngineError("rmsnorm: the norm after the sum needs its weight in float32 (float32_weight)");
+        Mat delta;
+        const Mat* d = nullptr;
+        if (stream.has_pending) {
+            delta = stream.pending.is_partials() ? ops::materialize(*rt->dev, stream.pending.part, rt->dtype) : stream.pending.m;
+            d = &delta;
+            stream.has_pending = false;
+        }
+        return ops::scale_add_rmsnorm(*rt->dev, stream.x, d, weight.m, residual_scale, eps, rt->dtype);
     }
     Mat forward(ResidualStream& stream, const int* rows, long long n_rows) override {
         Mat y = ops::add_rmsnorm(*rt->dev, stream.x, stream.has_pending ? &stream.pending : nullptr, weight.m, eps, rt->dtype, rows, n_rows,
@@ -161,28 +226,53 @@ struct RMSNorm : Norm {
 // src/kern/gpu/kernel_gpu.cu:343-371); here a table [position, rot/2, (cos, sin)] is computed once in
 // float64 and stored in float32, and the rotation is done in float32 inside the kernel that also
 // writes K and V into the cache.  theta (fixed to 10000 in the reference) and rot_dim are parameters.
-struct RopeHalf : PositionEncoding {
+//
+// "rope_pairs" is the same rotation with channel 2j paired with 2j + 1 (the interleaved layout).  Both
+// take an optional `scaling` {factor, original, fast, slow}: the frequencies are blended with the
+// stretched ones and cos and sin carry a magnitude factor (rotary_frequencies).
+struct RopeTable : PositionEncoding {
     int head_dim, rot_dim;
-    double theta;
+    double theta, magnitude = 1.0;
     long long max_positions;
+    bool pairs, scaled;
+    std::vector<double> freqs;
     std::shared_ptr<PositionTable> table;
-    RopeHalf(const PartSpec& s, Runtime* rt)
+    RopeTable(const PartSpec& s, Runtime* rt, bool pairs_)
             : PositionEncoding(s, rt), head_dim((int)s.get_int("head_dim")), rot_dim((int)s.get_int("rot_dim", s.get_int("head_dim"))),
-              theta(s.get_double("theta")), max_positions(s.get_int("max_positions")) {
+              theta(s.get_double("theta")), max_positions(s.get_int("max_positions")), pairs(pairs_), scaled(s.has("scaling")) {
         if (rot_dim % 2 || rot_dim <= 0 || rot_dim > head_dim)
-            throw ConfigError("rope_half: rot_dim " + std::to_string(rot_dim) + " must be even and in (0, head_dim]");
-        if (!(theta > 0) || max_positions <= 0) throw ConfigError("rope_half: theta and max_positions must be positive");
+            throw ConfigError(s.kind + ": rot_dim " + std::to_string(rot_dim) + " must be even and in (0, head_dim]");
+        if (!(theta > 0) || max_positions <= 0) throw ConfigError(s.kind + ": theta and max_positions must be positive");
+        const Json* sc = scaled ? &s.params.at("scaling") : nullptr;
+        freqs = rotary_frequencies(theta, rot_dim, sc, &magnitude);
     }
-    bool takes_partials() const override { return true; }
-    void prepare() override { table = shared_position_table(rt, theta, rot_dim, max_positions); }
+    bool takes_partials() const override { return !pairs; }
+    void prepare() override { table = shared_position_table(rt, freqs, magnitude, max_positions); }
     bool rotation_table(const float** t, int* rot, long long* n_pos) const override {
+        if (pairs) return false;
         *t = table ? table->data() : nullptr;
         *rot = rot_dim;
         *n_pos = max_positions;
         return true;
     }
+    bool table_rotation(const float** t, int* rot, long long* n_pos, bool* is_pairs) const override {
+        *t = table ? table->data() : nullptr;
+        *rot = rot_dim;
+        *n_pos = max_positions;
+        *is_pairs = pairs;
+        return true;
+    }
     Mat encode_and_store(const MatOrPartials& qkv, ops::Geometry g, const StepContext& ctx, const KVView& kv) override {
-        return ops::rope_kv_write(*rt->dev, qkv, table->data(), rot_dim, max_positions, ctx, kv, g);
+        if (!pairs) return ops::rope_kv_write(*rt->dev, qkv, table->data(), rot_dim, max_positions, ctx, kv, g);
+        ops::QkPrep p;
+        p.q_off = 0;
+        p.k_off = g.n_heads * g.head_dim;
+        p.v_off = (g.n_heads + g.n_kv_heads) * g.head_dim;
+        p.cos_sin = table->data();
+        p.rot_dim = rot_dim;
+        p.pairs = true;
+        p.n_pos = max_positions;
+        return ops::qk_prep(*rt->dev, qkv.is_partials() ? ops::materialize(*rt->dev, qkv.part, rt->dtype) : qkv.m, p, g, ctx, kv, rt->dtype);
     }
 };
 
@@ -212,29 +302,62 @@ struct NoPosition : PositionEncoding {
 // head (src/core/op.h:327-332); here the three matrices are stacked into one
 // [(heads + 2 kv heads) * d, H] at load so that one product feeds the rotation kernel, and the number
 // of KV heads, the head size and an optional window are parameters.
+//
+// Options beyond the reference's attention, each a parameter that is off unless given: `v_head_dim`
+// (values of another size than keys), `qkv_bias` (biases on the three projections), `qk_norm` =
+// "projection" (an RMS norm with a weight over the token's whole q projection, all heads together, and
+// likewise over k, before the rotation; `norm_eps`), `sink` (one learned number per head whose
+// exponential joins the softmax denominator without a value), `out_gate` = "head_sigmoid" (a
+// projection of the mixer's input to one number per head; the head's output is multiplied by its
+// sigmoid before the output projection), `own_kv` = false (the layer has no key and value
+// projections and attends to the keys and values another layer wrote into the cache entry it
+// reads), `scale`, `output_dtype` = "float32" (the output projection is not rounded to the compute
+// dtype, for a block that adds it to a float32 stream itself) and `names` (the tensors' names below
+// the part's prefix).  With any of the first six the layer takes the general path: one float32
+// product for q, k, v and the gate, one kernel for biases, norms, rotation and the cache write
+// (ops::qk_prep), and the general attention kernel, which knows sinks, gates and value sizes.
 struct Attention : Mixer {
     long long hidden;
-    int n_heads, n_kv_heads, head_dim, window;
-    float scale;
+    int n_heads, n_kv_heads, head_dim, v_head_dim, window;
+    float scale, norm_eps;
+    bool qkv_bias, proj_norm, has_sink, has_gate, own_kv, out_f32;
+    std::map<std::string, std::string> names;
     std::unique_ptr<PositionEncoding> position;
     DeviceBuffer qkv_buf, o_buf;
     Mat w_qkv, w_o;
+    OwnedMat b_q, b_k, b_v, n_q, n_k, sinks;
     Attention(const PartSpec& s, Runtime* rt)
             : Mixer(s, rt), hidden(s.get_int("hidden_size")), n_heads((int)s.get_int("n_heads")), n_kv_heads((int)s.get_int("n_kv_heads")),
-              head_dim((int)s.get_int("head_dim")), window((int)s.get_int("window", 0)) {
-        if (hidden <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || window < 0)
+              head_dim((int)s.get_int("head_dim")), v_head_dim((int)s.get_int("v_head_dim", s.get_int("head_dim"))),
+              window((int)s.get_int("window", 0)), norm_eps((float)s.get_double("norm_eps", 1e-6)), qkv_bias(s.get_bool("qkv_bias", false)),
+              proj_norm(s.get_string("qk_norm", "none") == "projection"), has_sink(s.get_bool("sink", false)),
+              has_gate(s.get_string("out_gate", "none") == "head_sigmoid"), own_kv(s.get_bool("own_kv", true)),
+              out_f32(s.get_string("output_dtype", "compute") == "float32") {
+        if (hidden <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || v_head_dim <= 0 || window < 0)
             throw ConfigError("attention: sizes must be positive");
         if (n_heads % n_kv_heads) throw ConfigError("attention: n_heads must be a multiple of n_kv_heads");
+        const std::string qn = s.get_string("qk_norm", "none"), og = s.get_string("out_gate", "none");
+        if (qn != "none" && qn != "projection") throw ConfigError("attention: qk_norm '" + qn + "' is not supported (none, projection)");
+        if (og != "none" && og != "head_sigmoid") throw ConfigError("attention: out_gate '" + og + "' is not supported (none, head_sigmoid)");
+        names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"}, {"o", "o_proj.weight"},
+                 {"q_bias", "q_proj.bias"}, {"k_bias", "k_proj.bias"}, {"v_bias", "v_proj.bias"}, {"q_norm", "q_norm.weight"},
+                 {"k_norm", "k_norm.weight"}, {"sink", "sinks"}, {"gate", "gate_proj.weight"}};
+        if (s.has("names"))
+            for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
         // the attention kernels read heads 16 bytes at a time: said when the model is built, not at its first step
-        if (rt && head_dim % 8)
+        if (rt && !general() && head_dim % 8)
             throw ConfigError("attention: head size " + std::to_string(head_dim) +
                               " is not supported by the kernels (multiples of 8 up to " + std::to_string(ops::kMaxHeadDimGeneric) + ")");
-        if (rt && head_dim > ops::kMaxHeadDimGeneric && !(head_dim == 64 || head_dim == 128))
+        if (rt && (head_dim > ops::kMaxHeadDimGeneric || v_head_dim > ops::kMaxHeadDimGeneric) && !(head_dim == 64 || head_dim == 128))
             throw ConfigError("attention: head size " + std::to_string(head_dim) + " is not supported by the kernels (up to " +
                               std::to_string(ops::kMaxHeadDimGeneric) + ")");
         scale = s.has("scale") ? (float)s.get_double("scale") : (float)(1.0 / std::sqrt((double)head_dim));
         position = build_position(s.get_part("position"), rt);
         if (rt) position->prepare();
+    }
+    // true if the layer needs the general path (see above)
+    bool general() const {
+        return v_head_dim != head_dim || qkv_bias || proj_norm || has_sink || has_gate || !own_kv || out_f32;
     }
     bool graph_safe() const override { return true; }     // a decode step's launches depend only on the batch size
     // Causal attention: tokens behind a sequence's real ones are seen by none of them.  Said only for
@@ -247,29 +370,111 @@ struct Attention : Mixer {
         return window == 0 && position->rotation_table(&t, &rot, &n);
     }
     TensorDecls tensors() const override {
-        const long long q = (long long)n_heads * head_dim, kv = (long long)n_kv_heads * head_dim;
-        return {{"q_proj.weight", TensorDecl{{q, hidden}}}, {"k_proj.weight", TensorDecl{{kv, hidden}}},
-                {"v_proj.weight", TensorDecl{{kv, hidden}}}, {"o_proj.weight", TensorDecl{{hidden, q}}}};
+        const long long q = (long long)n_heads * head_dim, k = (long long)n_kv_heads * head_dim, v = (long long)n_kv_heads * v_head_dim;
+        const long long o = (long long)n_heads * v_head_dim;
+        TensorDecls d;
+        auto nm = [&](const char* role) { return names.at(role); };
+        d.push_back({nm("q"), TensorDecl{{q, hidden}}});
+        if (qkv_bias) d.push_back({nm("q_bias"), TensorDecl{{q}}});
+        if (own_kv) {
+            d.push_back({nm("k"), TensorDecl{{k, hidden}}});
+            if (qkv_bias) d.push_back({nm("k_bias"), TensorDecl{{k}}});
+            d.push_back({nm("v"), TensorDecl{{v, hidden}}});
+            if (qkv_bias) d.push_back({nm("v_bias"), TensorDecl{{v}}});
+        }
+        if (proj_norm) {
+            d.push_back({nm("q_norm"), TensorDecl{{q}, "norm"}});
+            if (own_kv) d.push_back({nm("k_norm"), TensorDecl{{k}, "norm"}});
+        }
+        if (has_sink) d.push_back({nm("sink"), TensorDecl{{(long long)n_heads}}});
+        if (has_gate) d.push_back({nm("gate"), TensorDecl{{(long long)n_heads, hidden}}});
+        d.push_back({nm("o"), TensorDecl{{hidden, o}}});
+        return d;
     }
+    // rows of the packed matrix: q, then k and v (a layer with keys and values of its own), then the gate
+    long long q_rows() const { return (long long)n_heads * head_dim; }
+    long long k_rows() const { return own_kv ? (long long)n_kv_heads * head_dim : 0; }
+    long long v_rows() const { return own_kv ? (long long)n_kv_heads * v_head_dim : 0; }
+    long long packed_rows() const { return q_rows() + k_rows() + v_rows() + (has_gate ? n_heads : 0); }
     void load(TensorSource& src) override {
-        const long long q = (long long)n_heads * head_dim, kv = (long long)n_kv_heads * head_dim;
+        const long long q = q_rows(), k = k_rows(), v = v_rows(), all = packed_rows();
         const size_t es = dtype_size(rt->dtype);
-        qkv_buf = DeviceBuffer(rt->dev, (size_t)(q + 2 * kv) * hidden * es, "the packed Q/K/V matrix");
-        w_qkv = Mat{qkv_buf.get(), q + 2 * kv, hidden, rt->dtype, q + 2 * kv};
-        src.fetch_into("q_proj.weight", w_qkv.p, rt->dtype);
-        src.fetch_into("k_proj.weight", (char*)w_qkv.p + (size_t)q * hidden * es, rt->dtype);
-        src.fetch_into("v_proj.weight", (char*)w_qkv.p + (size_t)(q + kv) * hidden * es, rt->dtype);
-        o_buf = DeviceBuffer(rt->dev, (size_t)hidden * q * es, "the output matrix of an attention layer");
-        w_o = Mat{o_buf.get(), hidden, q, rt->dtype, hidden};
-        src.fetch_into("o_proj.weight", w_o.p, rt->dtype);
+        qkv_buf = DeviceBuffer(rt->dev, (size_t)all * hidden * es, "the packed Q/K/V matrix");
+        w_qkv = Mat{qkv_buf.get(), all, hidden, rt->dtype, all};
+        src.fetch_into(names.at("q"), w_qkv.p, rt->dtype);
+        if (own_kv) {
+            src.fetch_into(names.at("k"), (char*)w_qkv.p + (size_t)q * hidden * es, rt->dtype);
+            src.fetch_into(names.at("v"), (char*)w_qkv.p + (size_t)(q + k) * hidden * es, rt->dtype);
+        }
+        if (has_gate) src.fetch_into(names.at("gate"), (char*)w_qkv.p + (size_t)(q + k + v) * hidden * es, rt->dtype);
+        const long long o = (long long)n_heads * v_head_dim;
+        o_buf = DeviceBuffer(rt->dev, (size_t)hidden * o * es, "the output matrix of an attention layer");
+        w_o = Mat{o_buf.get(), hidden, o, rt->dtype, hidden};
+        src.fetch_into(names.at("o"), w_o.p, rt->dtype);
+        // the small vectors are used in float32 arithmetic and kept so
+        if (qkv_bias) {
+            b_q = fetch_owned(rt, src, names.at("q_bias"), DType::F32, "an attention bias");
+            if (own_kv) {
+                b_k = fetch_owned(rt, src, names.at("k_bias"), DType::F32, "an attention bias");
+                b_v = fetch_owned(rt, src, names.at("v_bias"), DType::F32, "an attention bias");
+            }
+        }
+        if (proj_norm) {
+            n_q = fetch_owned(rt, src, names.at("q_norm"), DType::F32, "a projection norm's weight");
+            if (own_kv) n_k = fetch_owned(rt, src, names.at("k_norm"), DType::F32, "a projection norm's weight");
+        }
+        if (has_sink) sinks = fetch_owned(rt, src, names.at("sink"), DType::F32, "the attention sinks");
     }
-    CacheRequest cache_request() const override { return CacheRequest::paged(n_kv_heads, head_dim, window); }
+    CacheRequest cache_request() const override {
+        return own_kv ? CacheRequest::paged(n_kv_heads, head_dim, window, v_head_dim) : CacheRequest();
+    }
+
+    MatOrPartials forward_general(const Mat& h, const StepContext& ctx, KVView kv) {
+        Device& dev = *rt->dev;
+        const ops::Geometry g{n_heads, n_kv_heads, head_dim};
+        if (kv.n_kv_heads != n_kv_heads || kv.head_dim != head_dim || (kv.v_head_dim > 0 ? kv.v_head_dim : kv.head_dim) != v_head_dim)
+            throw EngineError("attention: the cache entry's keys and values do not have this layer's head count and sizes");
+        if (!own_kv && kv.writes) throw EngineError("attention: a layer without key and value projections cannot write a cache entry");
+        Mat x = ops::linear(dev, rt->gemm, h, w_qkv, DType::F32, false).m;
+        ops::QkPrep p;
+        p.q_off = 0;
+        if (own_kv) {
+            p.k_off = (int)q_rows();
+            p.v_off = (int)(q_rows() + k_rows());
+        }
+        p.q_bias = (const float*)b_q.m.p;
+        p.k_bias = (const float*)b_k.m.p;
+        p.v_bias = (const float*)b_v.m.p;
+        p.q_norm = (const float*)n_q.m.p;
+        p.k_norm = (const float*)n_k.m.p;
+        p.eps = norm_eps;
+        const float* table = nullptr;
+        int rot = 0;
+        long long n_pos = 0;
+        bool pairs = false;
+        if (!position->table_rotation(&table, &rot, &n_pos, &pairs))
+            throw EngineError("attention: with biases, norms, sinks or gates the position encoding must be a table rotation");
+        p.cos_sin = table;
+        p.rot_dim = rot;
+        p.pairs = pairs;
+        p.n_pos = n_pos;
+        Mat q = ops::qk_prep(dev, x, p, g, ctx, kv, rt->dtype);
+        ops::AttentionExtras ex;
+        ex.sinks = (const float*)sinks.m.p;
+        if (has_gate) {
+            ex.gate = (const float*)x.p + (q_rows() + k_rows() + v_rows());
+            ex.gate_stride = (int)x.cols;
+        }
+        Mat o = ops::attention_generic(dev, q, kv, ctx, g, scale, &ex);
+        return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, false);
+    }
 
     MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool may_defer) override {
         if (cache.kind != CacheView::KV) throw EngineError("attention: the layer's cache entry holds no keys and values");
         Device& dev = *rt->dev;
         KVView kv = cache.kv;
         kv.writes = writes;
+        if (general()) return forward_general(h, ctx, kv);
         const ops::Geometry g{n_heads, n_kv_heads, head_dim};
         const float* table = nullptr;
         int rot = 0;
@@ -297,32 +502,43 @@ struct Attention : Mixer {
 // into one [2I, H] matrix at load, row 2i the gate row and row 2i + 1 the up row of output i, so that
 // one product feeds the activation, and where the package's own kernels run that product the
 // activation is their epilogue (ops::linear_gated).
+// `names` renames the three tensors; `output_dtype` = "float32" leaves the down projection unrounded.
 struct GatedMLP : FeedForward {
     long long hidden, inter;
+    bool out_f32;
+    std::string n_gate = "gate_proj.weight", n_up = "up_proj.weight", n_down = "down_proj.weight";
     DeviceBuffer gu_buf, down_buf;
     Mat w_gate_up, w_down;
-    GatedMLP(const PartSpec& s, Runtime* rt) : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")) {
+    GatedMLP(const PartSpec& s, Runtime* rt)
+            : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")),
+              out_f32(s.get_string("output_dtype", "compute") == "float32") {
         const std::string act = s.get_string("activation", "silu");
         if (act != "silu") throw ConfigError("gated_mlp: activation '" + act + "' is not supported (only 'silu')");
         if (hidden <= 0 || inter <= 0) throw ConfigError("gated_mlp: sizes must be positive");
+        if (s.has("names")) {
+            const Json& n = s.params.at("names");
+            if (n.has("gate")) n_gate = n.at("gate").as_string();
+            if (n.has("up")) n_up = n.at("up").as_string();
+            if (n.has("down")) n_down = n.at("down").as_string();
+        }
     }
     TensorDecls tensors() const override {
-        return {{"gate_proj.weight", TensorDecl{{inter, hidden}}}, {"up_proj.weight", TensorDecl{{inter, hidden}}},
-                {"down_proj.weight", TensorDecl{{hidden, inter}}}};
+        return {{n_gate, TensorDecl{{inter, hidden}}}, {n_up, TensorDecl{{inter, hidden}}}, {n_down, TensorDecl{{hidden, inter}}}};
     }
     void load(TensorSource& src) override {
         const size_t es = dtype_size(rt->dtype);
         gu_buf = DeviceBuffer(rt->dev, (size_t)2 * inter * hidden * es, "the packed gate/up matrix");
         w_gate_up = Mat{gu_buf.get(), 2 * inter, hidden, rt->dtype, 2 * inter};
-        src.fetch_into("gate_proj.weight", w_gate_up.p, rt->dtype, 2 * hidden);
-        src.fetch_into("up_proj.weight", (char*)w_gate_up.p + (size_t)hidden * es, rt->dtype, 2 * hidden);
+        src.fetch_into(n_gate, w_gate_up.p, rt->dtype, 2 * hidden);
+        src.fetch_into(n_up, (char*)w_gate_up.p + (size_t)hidden * es, rt->dtype, 2 * hidden);
         down_buf = DeviceBuffer(rt->dev, (size_t)hidden * inter * es, "the down matrix of a feed-forward layer");
         w_down = Mat{down_buf.get(), hidden, inter, rt->dtype, hidden};
-        src.fetch_into("down_proj.weight", w_down.p, rt->dtype);
+        src.fetch_into(n_down, w_down.p, rt->dtype);
     }
     MatOrPartials forward(const Mat& h, const StepContext&, bool may_defer) override {
         Device& dev = *rt->dev;
-        return ops::linear(dev, rt->gemm, ops::linear_gated(dev, rt->gemm, h, w_gate_up), w_down, rt->dtype, may_defer);
+        return ops::linear(dev, rt->gemm, ops::linear_gated(dev, rt->gemm, h, w_gate_up), w_down, out_f32 ? DType::F32 : rt->dtype,
+                           may_defer && !out_f32);
     }
 };
 
@@ -330,10 +546,12 @@ struct GatedMLP : FeedForward {
 // written as the float32 residual stream.
 struct Embedding : EmbeddingPart {
     long long vocab, hidden;
+    std::string tensor;         // the table's name below the part's prefix
     OwnedMat weight;
-    Embedding(const PartSpec& s, Runtime* rt) : EmbeddingPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")) {}
-    TensorDecls tensors() const override { return {{"weight", TensorDecl{{vocab, hidden}}}}; }
-    void load(TensorSource& src) override { weight = fetch_owned(rt, src, "weight", rt->dtype, "the embedding table"); }
+    Embedding(const PartSpec& s, Runtime* rt)
+            : EmbeddingPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), tensor(s.get_string("tensor", "weight")) {}
+    TensorDecls tensors() const override { return {{tensor, TensorDecl{{vocab, hidden}}}}; }
+    void load(TensorSource& src) override { weight = fetch_owned(rt, src, tensor, rt->dtype, "the embedding table"); }
     ResidualStream forward(const StepContext& ctx) override {
         ResidualStream s;
         s.dev = rt->dev;
@@ -349,17 +567,19 @@ struct Embedding : EmbeddingPart {
 struct LMHead : HeadPart {
     long long vocab, hidden;
     bool is_tied;
+    std::string tensor;
     OwnedMat own;
     Mat weight;
     LMHead(const PartSpec& s, Runtime* rt)
-            : HeadPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), is_tied(s.get_bool("tied", false)) {}
+            : HeadPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), is_tied(s.get_bool("tied", false)),
+              tensor(s.get_string("tensor", "weight")) {}
     TensorDecls tensors() const override {
         if (is_tied) return {};
-        return {{"weight", TensorDecl{{vocab, hidden}}}};
+        return {{tensor, TensorDecl{{vocab, hidden}}}};
     }
     void load(TensorSource& src) override {
         if (is_tied) return;
-        own = fetch_owned(rt, src, "weight", rt->dtype, "the output matrix");
+        own = fetch_owned(rt, src, tensor, rt->dtype, "the output matrix");
         weight = own.m;
     }
     bool tied() const override { return is_tied; }
@@ -384,9 +604,31 @@ struct PreNormBlock : Block {
     }
 };
 
+// "postnorm" is the norm-after-the-sum layer:
+//     x = norm1(a x + mixer(x));  x = norm2(a x + ffn(x))
+// The sublayers read the stream itself, and the normed sum replaces it; the factor a is the norms'
+// `residual_scale`.  "postnorm_mixer" is the same layer without a feed-forward (and without norm2).
+struct PostNormBlock : Block {
+    void forward(ResidualStream& stream, const StepContext& ctx, const CacheView& cache, bool writes) override {
+        if (!stream.h.p) {      // the first layer: the embedding's rows in the compute dtype
+            stream.flush();
+            stream.h = ops::cast(*stream.dev, stream.x, ctx.rt->dtype);
+        }
+        stream.add(mixer->forward(stream.h, ctx, cache, writes, false));
+        stream.h = norms.at("norm1")->forward_into_stream(stream);
+        if (!ffn) return;
+        stream.add(ffn->forward(stream.h, ctx, false));
+        stream.h = norms.at("norm2")->forward_into_stream(stream);
+    }
+};
+
 void register_builtin_parts() {
+    register_decay_parts(reg<Mixer>());
+    block_reg()["postnorm"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
+    block_reg()["postnorm_mixer"] = BlockKind{{"norm1"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
     reg<Norm>()["rmsnorm"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<Norm>(new RMSNorm(s, rt)); };
-    reg<PositionEncoding>()["rope_half"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new RopeHalf(s, rt)); };
+    reg<PositionEncoding>()["rope_half"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new RopeTable(s, rt, false)); };
+    reg<PositionEncoding>()["rope_pairs"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new RopeTable(s, rt, true)); };
     reg<PositionEncoding>()["none"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new NoPosition(s, rt)); };
     reg<Mixer>()["attention"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<Mixer>(new Attention(s, rt)); };
     reg<FeedForward>()["gated_mlp"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<FeedForward>(new GatedMLP(s, rt)); };

@@ -128,6 +128,7 @@ struct ResidualStream {
     Mat x;
     bool has_pending = false;
     MatOrPartials pending;
+    Mat h;      // the stream's rows in the compute dtype, where a block keeps them (norm after the sum); empty otherwise
     void add(const MatOrPartials& delta) {
         if (has_pending) flush();
         pending = delta;
@@ -148,6 +149,10 @@ public:
     // Fold the stream's pending addition in and return the normed rows in the compute dtype; `rows`
     // (int32, device) restricts it to those rows (the stream itself is then left as it is).
     virtual Mat forward(ResidualStream& stream, const int* rows, long long n_rows) = 0;
+    // Norm after the sum: stream.x <- norm(residual_scale * stream.x + pending), the norm's own
+    // residual_scale; the normed rows ARE the stream from then on, and they are also returned in the
+    // compute dtype for the sublayer that reads them next.  Only norms that can do this override it.
+    virtual Mat forward_into_stream(ResidualStream& stream) { throw EngineError("norm '" + spec.kind + "' cannot replace the stream by its output"); }
 };
 
 class PositionEncoding : public Part {
@@ -161,6 +166,14 @@ public:
     // Q and K head by angles from a cos/sin table float32 [positions, rot_dim / 2, 2] (rot_dim 0: nothing
     // at all), so that a mixer whose kernel can do that itself may skip encode_and_store.
     virtual bool rotation_table(const float** table, int* rot_dim, long long* n_pos) const { return false; }
+    // The same for either pairing of the channels: true if the encoding is a rotation of the first rot_dim
+    // channels of every head by table angles, *pairs saying whether channel 2j goes with 2j + 1 (true) or
+    // j with j + rot_dim / 2 (false).  A mixer with a kernel of its own between projection and attention
+    // (biases, norms) asks this and does the rotation there.
+    virtual bool table_rotation(const float** table, int* rot_dim, long long* n_pos, bool* pairs) const {
+        *pairs = false;
+        return rotation_table(table, rot_dim, n_pos);
+    }
     // Encode positions into the Q and K heads of the packed projection and store the new K and V in the
     // cache (if kv.writes).  Returns the matrix that holds the encoded queries in its first
     // heads * head_dim columns: qkv itself (encoded in place) or, for unreduced slices, a new one.
@@ -254,5 +267,12 @@ struct PositionTable {
     const float* data() const { return (const float*)buf.get(); }
 };
 std::shared_ptr<PositionTable> shared_position_table(Runtime* rt, double theta, int rot_dim, long long positions);
+// The general form: entry (p, j) = magnitude * (cos, sin)(p * freqs[j]), freqs of rot_dim / 2 pairs.
+std::shared_ptr<PositionTable> shared_position_table(Runtime* rt, const std::vector<double>& freqs, double magnitude, long long positions);
+// Frequencies theta^(-2j / rot_dim), optionally blended with the ones stretched by `factor` along a
+// linear ramp over the pair index (the "YaRN" scaling: pairs that turn more than `fast` times within
+// `original` positions keep their frequency, pairs that turn less than `slow` times are stretched);
+// *magnitude gets the factor 0.1 ln(factor) + 1 that goes with it (1 without scaling).
+std::vector<double> rotary_frequencies(double theta, int rot_dim, const Json* scaling, double* magnitude);
 
 }  // namespace illm

@@ -62,6 +62,8 @@ static int run(int argc, char** argv) {
     opt.dtype = dtype;
     opt.device_id = device;
     opt.max_tokens = max_tokens;
+    // no request can be longer than what all live requests hold together (whole pages)
+    opt.max_seq_len = (max_tokens + opt.page_size - 1) / opt.page_size * opt.page_size;
     std::unique_ptr<Engine> engine = Engine::from_folder(model, opt);
     std::map<std::string, int> slots;
     std::string line;
