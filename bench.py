@@ -143,6 +143,120 @@ def prefill_flops(cfg, n_layers, T, fig):
     return linear + attn
 
 
+# ---- beside the contract: the Vokelix design next to LLaMA layers of equal size (--design vokelix)
+
+DESIGN_SIZES = {          # width, feed-forward, heads, kv heads, head size (keys and values), heads of the linear layers
+    "1k": dict(width=1024, ff=2816, heads=8, kv=2, d=128, lin_heads=8, lin_d=128),
+    "2k": dict(width=2048, ff=5632, heads=16, kv=4, d=128, lin_heads=16, lin_d=128),
+    "4k": dict(width=4096, ff=11008, heads=32, kv=8, d=128, lin_heads=32, lin_d=128),
+}
+DESIGN_LAYERS = ("lightning", "attention", "retention", "attention_shared", "lightning", "retention")
+
+
+def vokelix_config(z, vocab=32000, max_positions=4096):
+    att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"], vdim=z["d"], scale=z["d"] ** -0.5,
+               rot=dict(base=250000.0, dims=z["d"] // 2, scaling=dict(factor=2.0, original=1024, fast=32.0, slow=1.0)))
+    layers, first_att = [], None
+    for i, t in enumerate(DESIGN_LAYERS):
+        mlp = dict(kind="dense", ff=z["ff"])
+        if t.startswith("attention"):
+            m = dict(att)
+            if t == "attention_shared":
+                m["kv_from"] = first_att
+            else:
+                first_att = i
+            layers.append(dict(type="attention", mixer=m, mlp=mlp))
+        else:
+            H = z["lin_heads"]
+            m = dict(heads=H, dim=z["lin_d"], vdim=z["lin_d"], decay=[1.0 - 2.0 ** -(5 + 5 * h / max(H - 1, 1)) for h in range(H)])
+            if t == "retention":
+                m["rot"] = dict(base=1000000.0, dims=z["lin_d"])
+            layers.append(dict(type=t, mixer=m, mlp=mlp))
+    return dict(architecture="Vokelix", layers=layers, norm=dict(eps=1e-6), postln_alpha=2.0, vocab=vocab, width=z["width"],
+                max_positions=max_positions)
+
+
+def llama_twin(z, vocab=32000, max_positions=4096):
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=len(DESIGN_LAYERS),
+                num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["d"], intermediate_size=z["ff"],
+                vocab_size=vocab, rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=max_positions,
+                tie_word_embeddings=False)
+
+
+def run_design(args):
+    """Prompt and decode throughput of the Vokelix design at a few layer sizes, each beside a LLaMA
+    model of the same width, feed-forward, head counts and number of layers, through Engine.step; and
+    where each of the two spends its time, kernel by kernel (the driver's activity records of one step).
+    One JSON line per (size, model)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from inferllm_b200 import Engine, EngineOptions, StepItem, config_from_dict
+    T, B, C = args.design_tokens, args.batch, args.design_context
+    K, W = args.steps, max(3, args.warmup)
+    g = torch.Generator().manual_seed(0)
+
+    def timed(fn, n):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def by_kernel(fn):
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        out = {}
+        for ev in prof.events():
+            if ev.device_type.name == "CUDA" and "memcpy" not in ev.name.lower() and "memset" not in ev.name.lower():
+                name = ev.name.split("<")[0].split("(")[0].replace("void ", "")
+                out[name] = out.get(name, 0.0) + ev.device_time
+        return {k: round(v, 1) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+    for size in args.design_size.split(","):
+        z = DESIGN_SIZES[size]
+        for which, cfgd in (("vokelix", vokelix_config(z)), ("llama", llama_twin(z))):
+            eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=B * (C + 64) + T + 64, max_seq_len=4096,
+                                                                           max_batch=max(B, 8)), seed=0)
+            ids = torch.randint(0, 32000, (T,), generator=g).tolist()
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([StepItem(s, ids, [T - 1])])
+                eng.end_sequence(s)
+
+            for _ in range(3):
+                prefill()
+            pf_ms = timed(prefill, 3)
+            pf_kernels = by_kernel(prefill)
+            slots = [eng.new_sequence() for _ in range(B)]
+            start = C - K - W - 2
+            for s in slots:
+                eng.step([StepItem(s, torch.randint(0, 32000, (start,), generator=g).tolist(), [])])
+
+            def one():
+                eng.step([StepItem(s, [5], [0]) for s in slots])
+
+            for _ in range(W):
+                one()
+            dec_kernels = by_kernel(one)
+            dec_ms = timed(one, K)
+            for s in slots:
+                eng.end_sequence(s)
+            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else len(DESIGN_LAYERS),
+                              "prefill_tokens": T, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(T / pf_ms * 1e3, 1),
+                              "decode_batch": B, "decode_context": C, "decode_ms": round(dec_ms, 4),
+                              "decode_tok_s": round(B / dec_ms * 1e3, 1), "prefill_kernels_us": pf_kernels,
+                              "decode_kernels_us": dec_kernels}), flush=True)
+            del eng
+            torch.cuda.empty_cache()
+    return 0
+
+
 SCENARIOS = {"8b": "16:64:2048:256", "13b": "32:128:1024:to4096", "7b": "8:512:512:256"}
 REF_LIKE_LAYERS = 4            # layers of the model that the reference arm runs (baseline/reference_arm.py)
 
@@ -366,8 +480,15 @@ def main():
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
                     "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
+    ap.add_argument("--design", choices=["vokelix"], help="beside the contract: prompt and decode throughput of this design "
+                    "at a few layer sizes, each next to LLaMA layers of equal size, with the time per kernel")
+    ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
+    ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")
+    ap.add_argument("--design-context", type=int, default=2048, help="with --design: position at which the timed decode steps end")
     args = ap.parse_args()
 
+    if args.design:
+        return run_design(args)
     if args.gpus != 1:
         print(f"bench.py: inferllm_b200 is a single-GPU library; --gpus {args.gpus} is not supported (N=1 only)")
         return 2

@@ -178,7 +178,9 @@ template <int D>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc,
                                               const float* __restrict__ part_ml,
                                               const int* __restrict__ token_pos, bf16* __restrict__ out,
-                                              int n_chunks, int nh, int window, int chunk_keys) {
+                                              int n_chunks, int nh, int window, int chunk_keys,
+                                              const float* __restrict__ sinks, const float* __restrict__ gate,
+                                              int gate_stride) {
     pdl_grid_sync();
     const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
     const int p = token_pos[t];
@@ -201,30 +203,47 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_acc
         den += part_ml[(o + ch) * 2 + 1] * w;
         num += part_acc[(o + ch) * D + c] * w;
     }
-    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(num / den);
+    if (sinks) {
+        // one more term of the softmax denominator, without a value: exp(sink - max); the partial maxima
+        // are in units of log2
+        const float s2 = sinks[h] * 1.4426950408889634f;
+        if (s2 <= M) {
+            den += exp2f(s2 - M);
+        } else {
+            const float w = exp2f(M - s2);
+            den = den * w + 1.0f;
+            num *= w;
+        }
+    }
+    float r = num / den;
+    if (gate) r *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + h]));      // the head's output gate
+    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(r);
 }
 
 template <int D, int G>
 static int launch(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table,
                   int max_pages, const int* token_pos, const int* token_seq, float* part_acc,
                   float* part_ml, void* out, int T, int nh, int nkv, int page_size, int window,
-                  float scale, int n_chunks, cudaStream_t s) {
+                  float scale, int n_chunks, const float* sinks, const float* gate, int gate_stride, cudaStream_t s) {
     dim3 grid(n_chunks, nkv, T);
     illm_launch(attention_decode_kernel<D, G>, dim3(grid), dim3(AD_THREADS), 0, s, 
         (const bf16*)q, q_stride, (const bf16*)kc, (const bf16*)vc, block_table, max_pages, token_pos,
         token_seq, part_acc, part_ml, n_chunks, nh, nkv, page_size, window, scale * 1.4426950408889634f);
     illm_launch(attention_decode_merge_kernel<D>, dim3(dim3(nh, T)), dim3(D), 0, s, part_acc, part_ml, token_pos, (bf16*)out,
-                                                             n_chunks, nh, window, AD_CHUNK);
+                                                             n_chunks, nh, window, AD_CHUNK, sinks, gate, gate_stride);
     return illm_launch_status();
 }
 
 // Scratch: part_acc float [T, nh, n_chunks, D], part_ml float [T, nh, n_chunks, 2], with
 // n_chunks = ceil(max_len / 256) for the longest sequence the launch may meet.
-extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc, const void* vc,
-                                     const int* block_table, int max_pages, const int* token_pos,
-                                     const int* token_seq, float* part_acc, float* part_ml, void* out,
-                                     int T, int nh, int nkv, int d, int page_size, int window,
-                                     float scale, int n_chunks, void* stream) {
+// The same with a sink per head in the softmax denominator (float32 [nh]) and a sigmoid gate per
+// (token, head) on the output (float32, gate[t * gate_stride + h]); either may be nullptr.
+extern "C" int illm_attention_decode_ex(const void* q, int q_stride, const void* kc, const void* vc,
+                                        const int* block_table, int max_pages, const int* token_pos,
+                                        const int* token_seq, float* part_acc, float* part_ml, void* out,
+                                        int T, int nh, int nkv, int d, int page_size, int window,
+                                        float scale, int n_chunks, const float* sinks, const float* gate, int gate_stride,
+                                        void* stream) {
     if (T <= 0) return 0;
     if (nkv <= 0 || nh % nkv || page_size % AD_U || T > 65535 || nkv > 65535 || d <= 0 || n_chunks <= 0)
         return ILLM_ERR_BAD_ARG;
@@ -236,11 +255,21 @@ extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc
 #define AD_CASE(DD, GG)                                                                            \
     if (d == DD && g == GG)                                                                        \
         return launch<DD, GG>(q, q_stride, kc, vc, block_table, max_pages, token_pos, token_seq,  \
-                              part_acc, part_ml, out, T, nh, nkv, page_size, window, scale, n_chunks, s);
+                              part_acc, part_ml, out, T, nh, nkv, page_size, window, scale, n_chunks, sinks, gate, \
+                              gate_stride, s);
     AD_CASE(128, 1) AD_CASE(128, 2) AD_CASE(128, 4) AD_CASE(128, 8)
     AD_CASE(64, 1) AD_CASE(64, 2) AD_CASE(64, 3) AD_CASE(64, 4) AD_CASE(64, 8)
 #undef AD_CASE
     return ILLM_ERR_BAD_ARG;
+}
+
+extern "C" int illm_attention_decode(const void* q, int q_stride, const void* kc, const void* vc,
+                                     const int* block_table, int max_pages, const int* token_pos,
+                                     const int* token_seq, float* part_acc, float* part_ml, void* out,
+                                     int T, int nh, int nkv, int d, int page_size, int window,
+                                     float scale, int n_chunks, void* stream) {
+    return illm_attention_decode_ex(q, q_stride, kc, vc, block_table, max_pages, token_pos, token_seq, part_acc, part_ml, out, T, nh, nkv, d,
+                                    page_size, window, scale, n_chunks, nullptr, nullptr, 0, stream);
 }
 
 // The merge alone, for kernels that write the same partial layout with chunks of another size
@@ -252,10 +281,10 @@ extern "C" int illm_attention_decode_merge(const float* part_acc, const float* p
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 128)
         illm_launch(attention_decode_merge_kernel<128>, dim3(nh, T), dim3(128), 0, s, part_acc, part_ml, token_pos,
-                    (bf16*)out, n_chunks, nh, window, chunk_keys);
+                    (bf16*)out, n_chunks, nh, window, chunk_keys, nullptr, nullptr, 0);
     else if (d == 64)
         illm_launch(attention_decode_merge_kernel<64>, dim3(nh, T), dim3(64), 0, s, part_acc, part_ml, token_pos,
-                    (bf16*)out, n_chunks, nh, window, chunk_keys);
+                    (bf16*)out, n_chunks, nh, window, chunk_keys, nullptr, nullptr, 0);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();

@@ -180,13 +180,20 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-template <int D>
+// WIDE_P: the softmax weights enter the product with V as two bfloat16 terms, P = P1 + P2 with
+// P2 = P - P1 rounded again (sixteen bits of mantissa instead of eight): P2 lies in the other half of
+// the S block's columns and P V is issued once more with it.  For mixers whose softmax weights are to
+// stay float32; the plain attention passes false and is compiled as before.  `sinks` (float32 [nh]):
+// one more term exp(sink) of the row's denominator, without a value; `gate` (float32,
+// gate[row * gate_stride + head]): the head's output is multiplied by its sigmoid.  Either may be nullptr.
+template <int D, bool WIDE_P>
 __global__ void __launch_bounds__(FT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
                             int max_pages, const int* __restrict__ cu_q, const int* __restrict__ seq_lens,
                             bf16* __restrict__ out, int nh, int nkv, int page_size, int window,
-                            float scale_log2e, int* __restrict__ err) {
+                            float scale_log2e, int* __restrict__ err, const float* __restrict__ sinks,
+                            const float* __restrict__ gate, int gate_stride) {
     constexpr int FT_MMA_WARP = 4, FT_TMA_WARP = 5;
     constexpr int NA = D / 64;                            // 64-channel atoms of the head
     constexpr unsigned Q_TILE = FT_BM * D * 2;            // the query tile: [NA][128 rows][128 B]
@@ -332,6 +339,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int ks = 0; ks < FT_BN / 16; ks++)
                     mma_bf16_ts(tmem + O_COL, tmem + (i & 1) * S_COLS + ks * 8,
                                 desc_mnmajor(v_s + st * KV_BYTES + ks * 16 * 128, KV_ATOM), IDESC_O, (i > 0 || ks > 0) ? 1u : 0u);
+                if (WIDE_P) {
+#pragma unroll
+                    for (int ks = 0; ks < FT_BN / 16; ks++)
+                        mma_bf16_ts(tmem + O_COL, tmem + (i & 1) * S_COLS + FT_BN / 2 + ks * 8,
+                                    desc_mnmajor(v_s + st * KV_BYTES + ks * 16 * 128, KV_ATOM), IDESC_O, 1u);
+                }
                 mma_commit(v_empty0 + 8 * st);
                 mma_commit(pv_done);
             }
@@ -415,6 +428,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 psb = f2_add(psb, f2_pack(p2, p3));
                 pr[c >> 1] = pack_bf16(p0, p1);
                 pr[(c >> 1) + 1] = pack_bf16(p2, p3);
+                if (WIDE_P) {       // what the rounding took away, kept where the scores were
+                    sr[c] = __float_as_uint(p0 - __uint_as_float(pr[c >> 1] << 16));
+                    sr[c + 1] = __float_as_uint(p1 - __uint_as_float(pr[c >> 1] & 0xffff0000u));
+                    sr[c + 2] = __float_as_uint(p2 - __uint_as_float(pr[(c >> 1) + 1] << 16));
+                    sr[c + 3] = __float_as_uint(p3 - __uint_as_float(pr[(c >> 1) + 1] & 0xffff0000u));
+                }
             }
             {
                 float a0, a1, b0, b1;
@@ -423,6 +442,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 l_run += (a0 + a1) + (b0 + b1);
             }
             tmem_st32(s_addr, pr);
+            if (WIDE_P) {
+                tmem_wait_st();         // pr is written again
+#pragma unroll
+                for (int c = 0; c < FT_BN; c += 2) pr[c >> 1] = pack_bf16(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+                tmem_st32(s_addr + FT_BN / 2, pr);
+            }
             tmem_wait_st();
             // the prompt's last block may hold positions beyond the sequence: whatever the cache
             // has there must not reach the product (0 x NaN), so those rows of V are cleared
@@ -450,7 +475,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (alive && n_blocks > 0) alive = __all_sync(0xffffffffu, bar_wait(pv_done, (n_blocks - 1) & 1, err));
         if (alive && n_blocks > 0) {
             fence_after();
-            const float inv = 1.0f / l_run;
+            float inv;
+            if (sinks) {
+                // the sink's term relative to the row's reference (both in units of log2), whichever is larger
+                const float s2 = sinks[h] * 1.4426950408889634f;
+                if (s2 <= m_ref) {
+                    inv = 1.0f / (l_run + exp2f(s2 - m_ref));
+                } else {
+                    const float w = exp2f(m_ref - s2);
+                    inv = w / (l_run * w + 1.0f);
+                }
+            } else {
+                inv = 1.0f / l_run;
+            }
+            if (gate && r < rows) inv *= 1.0f / (1.0f + expf(-gate[(size_t)(q0 + row0 + r) * gate_stride + h]));
             bf16* dst = out + ((size_t)(q0 + row0 + r) * nh + h) * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
@@ -509,10 +547,11 @@ static int ft_make_map(CUtensorMap* map, const void* ptr, long long rows, long l
     return r == CUDA_SUCCESS ? 0 : ILLM_ERR_BAD_ARG;
 }
 
-template <int D>
+template <int D, bool WIDE_P>
 static int ft_launch(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages,
                      const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B,
-                     int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, cudaStream_t s) {
+                     int max_q, int nh, int nkv, int page_size, int window, float scale, int* err, const float* sinks,
+                     const float* gate, int gate_stride, cudaStream_t s) {
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = ft_make_map(&mq, q, T, (long long)nh * D, q_stride, FT_BM)) != 0) return rc;
@@ -521,32 +560,41 @@ static int ft_launch(const void* q, int q_stride, int T, const void* kc, const v
     if ((rc = ft_make_map(&mv, vc, kv_rows, D, D, FT_BN)) != 0) return rc;
     const size_t smem = (size_t)FT_BM * D * 2 + (size_t)(FT_KSTAGES + FT_VSTAGES) * FT_BN * D * 2 +
                         256;   // + barriers and the tensor-memory address
-    auto kern = attention_prefill_tc_kernel<D>;
+    auto kern = attention_prefill_tc_kernel<D, WIDE_P>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(nh, (max_q + FT_BM - 1) / FT_BM, B);
     illm_launch(kern, grid, dim3(FT_THREADS), smem, s, mq, mk, mv, block_table, max_pages, cu_q, seq_lens,
-                (bf16*)out, nh, nkv, page_size, window, scale * 1.4426950408889634f, err);
+                (bf16*)out, nh, nkv, page_size, window, scale * 1.4426950408889634f, err, sinks, gate, gate_stride);
     return illm_launch_status();
 }
 
 // q: the packed projection [T, q_stride] whose first nh*d columns are the query heads;
-// kc, vc: one cache entry [n_pages, nkv, page_size, d].
-extern "C" int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc, const void* vc,
-                                         long long n_pages, const int* block_table, int max_pages,
-                                         const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh,
-                                         int nkv, int d, int page_size, int window, float scale, int* err,
-                                         void* stream) {
+// kc, vc: one cache entry [n_pages, nkv, page_size, d].  wide_p, sinks, gate: see the kernel.
+extern "C" int illm_attention_prefill_tc_ex(const void* q, int q_stride, int T, const void* kc, const void* vc,
+                                            long long n_pages, const int* block_table, int max_pages,
+                                            const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh,
+                                            int nkv, int d, int page_size, int window, float scale, int* err,
+                                            int wide_p, const float* sinks, const float* gate, int gate_stride, void* stream) {
     if (B <= 0 || max_q <= 0) return 0;
     if (nkv <= 0 || nh % nkv || max_q > 65535 * FT_BM || B > 65535 || (q_stride & 7) || page_size % 64 ||
         ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15))
         return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (d == 128)
-        return ft_launch<128>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
-                              nh, nkv, page_size, window, scale, err, s);
-    if (d == 64)
-        return ft_launch<64>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q,
-                             nh, nkv, page_size, window, scale, err, s);
+#define FT_CASE(DD, WW)                                                                                                   \
+    if (d == DD && (wide_p != 0) == WW)                                                                                   \
+        return ft_launch<DD, WW>(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q, \
+                                 nh, nkv, page_size, window, scale, err, sinks, gate, gate_stride, s);
+    FT_CASE(128, false) FT_CASE(64, false) FT_CASE(128, true) FT_CASE(64, true)
+#undef FT_CASE
     return ILLM_ERR_BAD_ARG;
+}
+
+extern "C" int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc, const void* vc,
+                                         long long n_pages, const int* block_table, int max_pages,
+                                         const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh,
+                                         int nkv, int d, int page_size, int window, float scale, int* err,
+                                         void* stream) {
+    return illm_attention_prefill_tc_ex(q, q_stride, T, kc, vc, n_pages, block_table, max_pages, cu_q, seq_lens, out, B, max_q, nh, nkv, d,
+                                        page_size, window, scale, err, 0, nullptr, nullptr, 0, stream);
 }

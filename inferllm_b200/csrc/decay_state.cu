@@ -10,26 +10,34 @@
 // float32; a step loads it, runs its tokens in order and stores it, so prompts, portions of
 // prompts and single tokens are the same code and carry the same bits from step to step.
 //
-// decay_scan_kernel: one block per (sequence, head).  The state sits in shared memory for the
-// step; the step's tokens come in tiles of DS_TILE, prepared (activation, rotation, factor) by all
-// threads; then the tokens of the tile run one after the other: thread (r, j) owns rows r, r + R, ..
-// of column j, updates them and adds up its part of o_t[j]; the R parts are added in a fixed order.
+// decay_prep_kernel: activation, rotation and factor, in place on the projection's q, k and v
+// columns (one thread per rotated pair, so nothing is read after it was written).
 //
-// decay_chunk_kernel: the same recurrence for prompts in chunks of DC_C tokens on the tensor cores'
-// float32-accumulating warp MMAs is not what this file does: everything here is float32 FMA, so that
-// the float32 mode and the bfloat16 mode share one implementation of the recurrence, which the
-// design asks to be float32 in both.
+// decay_scan_kernel: the columns of S evolve independently of one another (S[:, j] only ever meets
+// v[j]), so a block owns one (sequence, head, group of columns) and a thread keeps its part of the
+// state in registers for the whole step: 32 rows of one column, the rows of a column dealt to LI
+// neighbouring lanes (LI = d / 32 rounded up to a power of two, rows beyond d are zeros).  The step's
+// tokens come in tiles through two shared-memory buffers filled by cp.async, the next tile on its
+// way while this one is used; every thread runs a tile's tokens one after the other without any
+// synchronisation: 32 independent chains s = decay s + k v[j], its part of o_t[j] = sum_i s q[i], and
+// a fixed tree of shuffles over the LI lanes of the column.  What bounds it is the float32 FMA rate
+// and the latency of the chain, not memory; a prompt of one sequence fills heads x dv / (128 / LI)
+// blocks.  The state is stored column by column ([slots, heads, dv, d]), so that a thread's rows are
+// 16-byte pieces.
+//
+// The recurrence is float32 throughout, in the float32 mode and in the bfloat16 mode alike, because
+// that is what such layers ask for (a state that is rounded to sixteen bits forgets).
 //
 // group_norm_gate_kernel: what follows the recurrence in such mixers: an RMS norm over groups of the
 // concatenated heads (one group = all heads together, with a weight; or one group per head, without),
 // times an activation of a gate projection (sigmoid or silu), rounded once to the activation dtype.
 #include "common.cuh"
 
-#define DS_TILE 16
-#define DS_THREADS 256
+#define DS_THREADS 128
+#define DS_MAX_TILE 16
 
 struct DecayScanArgs {
-    const float* x;
+    float* x;
     int ld, q_off, k_off, v_off;
     int nh, d, dv;
     int qk_act, v_act;              // 0: none, 1: silu
@@ -37,10 +45,12 @@ struct DecayScanArgs {
     int rot, n_pos;
     float k_scale;
     const float* decay;             // [nh]
-    float* state;                   // [slots, nh, d, dv]
+    float* state;                   // [slots, nh, dv, d]
     const int *slots, *cu_q, *token_pos;
     float* out;                     // [T, nh * dv]
     int* err;
+    int tile;                       // tokens staged at a time
+    int vec;                        // 16-byte copies are possible
 };
 
 __device__ __forceinline__ float act_of(float v, int act) {
@@ -49,100 +59,186 @@ __device__ __forceinline__ float act_of(float v, int act) {
     return v;
 }
 
-__global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
+__global__ void __launch_bounds__(128) decay_prep_kernel(DecayScanArgs a) {
     pdl_grid_sync();
-    extern __shared__ float sm[];
-    const int b = blockIdx.x, h = blockIdx.y;
-    const int d = a.d, dv = a.dv;
-    float* S = sm;                          // [d][dv]
-    float* qt = S + (size_t)d * dv;         // [DS_TILE][d]
-    float* kt = qt + DS_TILE * d;           // [DS_TILE][d]
-    float* vt = kt + DS_TILE * d;           // [DS_TILE][dv]
-    float* red = vt + DS_TILE * dv;         // [R][dv]
-    // columns per pass and row groups: a function of dv alone
-    const int J = dv < DS_THREADS ? ((dv + 31) & ~31) : DS_THREADS;
-    const int R = DS_THREADS / J;
-    const int r = threadIdx.x / J, jj = threadIdx.x % J;
-    const float dec = a.decay[h];
-    float* Sg = a.state + ((size_t)a.slots[b] * a.nh + h) * (size_t)d * dv;
-    for (int i = threadIdx.x; i < d * dv; i += DS_THREADS) S[i] = Sg[i];
-    const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+    const int t = blockIdx.x, h = blockIdx.y;
+    float* row = a.x + (size_t)t * a.ld;
+    float* q = row + a.q_off + h * a.d;
+    float* k = row + a.k_off + h * a.d;
     const int half = a.rot >> 1;
-    for (int tb = t0; tb < t1; tb += DS_TILE) {
-        const int n = t1 - tb < DS_TILE ? t1 - tb : DS_TILE;
-        __syncthreads();        // the previous tile has been used (and S is loaded)
-        for (int i = threadIdx.x; i < n * d; i += DS_THREADS) {
-            const int tt = i / d, c = i - tt * d;
-            const float* row = a.x + (size_t)(tb + tt) * a.ld;
-            float q = act_of(row[a.q_off + h * d + c], a.qk_act);
-            float k = act_of(row[a.k_off + h * d + c], a.qk_act);
-            if (c < a.rot) {
-                int p = a.token_pos[tb + tt];
-                if (p < 0 || p >= a.n_pos) {
-                    atomicExch(a.err, 3);
-                    p = 0;
-                }
-                const bool first = c < half;
-                const int j = first ? c : c - half, partner = first ? c + half : c - half;
-                const float cs = a.cos_sin[((size_t)p * half + j) * 2], sn = a.cos_sin[((size_t)p * half + j) * 2 + 1];
-                const float q2 = act_of(row[a.q_off + h * d + partner], a.qk_act);
-                const float k2 = act_of(row[a.k_off + h * d + partner], a.qk_act);
-                q = first ? q * cs - q2 * sn : q * cs + q2 * sn;
-                k = first ? k * cs - k2 * sn : k * cs + k2 * sn;
-            }
-            qt[i] = q;
-            kt[i] = k * a.k_scale;
-        }
-        for (int i = threadIdx.x; i < n * dv; i += DS_THREADS) {
-            const int tt = i / dv, c = i - tt * dv;
-            vt[i] = act_of(a.x[(size_t)(tb + tt) * a.ld + a.v_off + h * dv + c], a.v_act);
-        }
-        __syncthreads();
-        for (int tt = 0; tt < n; tt++) {
-            const float* q = qt + tt * d;
-            const float* k = kt + tt * d;
-            const float* v = vt + tt * dv;
-            for (int j = jj; j < dv; j += J) {
-                const float vj = v[j];
-                float part = 0.f;
-                if (r < R)
-                    for (int i = r; i < d; i += R) {
-                        const float s = dec * S[i * dv + j] + k[i] * vj;
-                        S[i * dv + j] = s;
-                        part = fmaf(s, q[i], part);
-                    }
-                if (r < R) red[r * dv + j] = part;
-            }
-            __syncthreads();
-            for (int j = threadIdx.x; j < dv; j += DS_THREADS) {
-                float o = 0.f;
-                for (int rr = 0; rr < R; rr++) o += red[rr * dv + j];
-                a.out[(size_t)(tb + tt) * a.nh * dv + (size_t)h * dv + j] = o;
-            }
-            __syncthreads();
+    int p = a.rot ? a.token_pos[t] : 0;
+    if (a.rot && (p < 0 || p >= a.n_pos)) {
+        if (threadIdx.x == 0) atomicExch(a.err, 3);
+        p = 0;
+    }
+    for (int c = threadIdx.x; c < a.d; c += blockDim.x) {
+        if (c < half) {
+            const float cs = a.cos_sin[((size_t)p * half + c) * 2], sn = a.cos_sin[((size_t)p * half + c) * 2 + 1];
+            const float q1 = act_of(q[c], a.qk_act), q2 = act_of(q[c + half], a.qk_act);
+            const float k1 = act_of(k[c], a.qk_act), k2 = act_of(k[c + half], a.qk_act);
+            q[c] = q1 * cs - q2 * sn;
+            q[c + half] = q2 * cs + q1 * sn;
+            k[c] = (k1 * cs - k2 * sn) * a.k_scale;
+            k[c + half] = (k2 * cs + k1 * sn) * a.k_scale;
+        } else if (c >= a.rot) {
+            q[c] = act_of(q[c], a.qk_act);
+            k[c] = act_of(k[c], a.qk_act) * a.k_scale;
         }
     }
+    if (a.v_act) {
+        float* v = row + a.v_off + h * a.dv;
+        for (int c = threadIdx.x; c < a.dv; c += blockDim.x) v[c] = act_of(v[c], a.v_act);
+    }
+}
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int LI>
+__global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
+    pdl_grid_sync();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int JW = 32 / LI;                     // columns per warp
+    constexpr int JB = JW * (DS_THREADS / 32);      // columns per block
+    constexpr int DP = 32 * LI;                     // rows with padding
+    constexpr int ROW = 2 * DP + JB;                // floats of one staged token: q, k, v
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * JB;
+    const int d = a.d, dv = a.dv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane % LI, jl = warp * JW + lane / LI;
+    const int j = j0 + jl;
+    const bool col_ok = j < dv;
+    const int jn = dv - j0 < JB ? dv - j0 : JB;     // columns of this block that exist
+    const float dec = a.decay[h];
+    float* Sg = a.state + ((size_t)a.slots[b] * a.nh + h) * (size_t)d * dv + (size_t)j * d;       // this thread's column
+    // row of register (m, c): m * 4 LI + 4 g + c, so that the LI lanes of a column read 16-byte pieces
+    // of q, k and the state that lie side by side
+    float s[8][4];
+#pragma unroll
+    for (int m = 0; m < 8; m++) {
+        const int i = m * 4 * LI + 4 * g;
+        if (a.vec && col_ok && i < d) {
+            const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
+            s[m][0] = v4.x; s[m][1] = v4.y; s[m][2] = v4.z; s[m][3] = v4.w;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; c++) s[m][c] = (col_ok && i + c < d) ? Sg[i + c] : 0.f;
+        }
+    }
+    // rows beyond d and columns beyond dv stay zero in both buffers
+    for (int idx = threadIdx.x; idx < 2 * a.tile * ROW; idx += DS_THREADS) sm[idx] = 0.f;
     __syncthreads();
-    for (int i = threadIdx.x; i < d * dv; i += DS_THREADS) Sg[i] = S[i];
+    const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
+    auto stage = [&](int buf, int tb) {
+        const int n = t1 - tb < a.tile ? t1 - tb : a.tile;
+        float* base = sm + buf * a.tile * ROW;
+        if (a.vec) {
+            const int cq = d >> 2, cv = jn >> 2, per = 2 * cq + cv;
+            for (int idx = threadIdx.x; idx < n * per; idx += DS_THREADS) {
+                const int tt = idx / per, c = idx - tt * per;
+                const float* row = a.x + (size_t)(tb + tt) * a.ld;
+                float* dst = base + tt * ROW;
+                if (c < cq) cp_async16(dst + 4 * c, row + a.q_off + h * d + 4 * c);
+                else if (c < 2 * cq) cp_async16(dst + DP + 4 * (c - cq), row + a.k_off + h * d + 4 * (c - cq));
+                else cp_async16(dst + 2 * DP + 4 * (c - 2 * cq), row + a.v_off + h * dv + j0 + 4 * (c - 2 * cq));
+            }
+        } else {
+            const int per = 2 * d + jn;
+            for (int idx = threadIdx.x; idx < n * per; idx += DS_THREADS) {
+                const int tt = idx / per, c = idx - tt * per;
+                const float* row = a.x + (size_t)(tb + tt) * a.ld;
+                float* dst = base + tt * ROW;
+                if (c < d) dst[c] = row[a.q_off + h * d + c];
+                else if (c < 2 * d) dst[DP + c - d] = row[a.k_off + h * d + c - d];
+                else dst[2 * DP + c - 2 * d] = row[a.v_off + h * dv + j0 + c - 2 * d];
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (t0 < t1) stage(0, t0);
+    int buf = 0;
+    for (int tb = t0; tb < t1; tb += a.tile, buf ^= 1) {
+        const int n = t1 - tb < a.tile ? t1 - tb : a.tile;
+        if (tb + a.tile < t1) {
+            stage(buf ^ 1, tb + a.tile);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const float* base = sm + buf * a.tile * ROW;
+        for (int tt = 0; tt < n; tt++) {
+            const float4* q4 = reinterpret_cast<const float4*>(base + tt * ROW) + g;
+            const float4* k4 = reinterpret_cast<const float4*>(base + tt * ROW + DP) + g;
+            const float vj = base[tt * ROW + 2 * DP + jl];
+            float part0 = 0.f, part1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < 8; m++) {
+                const float4 kk = k4[m * LI], qq = q4[m * LI];
+                s[m][0] = fmaf(dec, s[m][0], kk.x * vj);
+                s[m][1] = fmaf(dec, s[m][1], kk.y * vj);
+                s[m][2] = fmaf(dec, s[m][2], kk.z * vj);
+                s[m][3] = fmaf(dec, s[m][3], kk.w * vj);
+                part0 = fmaf(s[m][0], qq.x, part0);
+                part1 = fmaf(s[m][1], qq.y, part1);
+                part0 = fmaf(s[m][2], qq.z, part0);
+                part1 = fmaf(s[m][3], qq.w, part1);
+            }
+            float part = part0 + part1;
+#pragma unroll
+            for (int o = 1; o < LI; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (g == 0 && col_ok) a.out[(size_t)(tb + tt) * a.nh * dv + (size_t)h * dv + j] = part;
+        }
+        __syncthreads();        // the buffer is filled again by the tile after the next
+    }
+#pragma unroll
+    for (int m = 0; m < 8; m++) {
+        const int i = m * 4 * LI + 4 * g;
+        if (a.vec && col_ok && i < d) {
+            *reinterpret_cast<float4*>(Sg + i) = make_float4(s[m][0], s[m][1], s[m][2], s[m][3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                if (col_ok && i + c < d) Sg[i + c] = s[m][c];
+        }
+    }
 }
 
+// head sizes up to 1024
 extern "C" long long illm_decay_scan_smem(int d, int dv) {
-    const int J = dv < DS_THREADS ? ((dv + 31) & ~31) : DS_THREADS;
-    const int R = DS_THREADS / J;
-    return ((long long)d * dv + 2LL * DS_TILE * d + (long long)DS_TILE * dv + (long long)R * dv) * (long long)sizeof(float);
+    (void)dv;
+    return d <= 1024 ? 40 * 1024 : (1LL << 40);
 }
 
-extern "C" int illm_decay_scan(const float* x, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act,
+template <int LI>
+static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
+    constexpr int DP = 32 * LI, JB = (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
+    int tile = (int)(40 * 1024 / sizeof(float) / (2 * ROW));
+    a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
+    const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    illm_launch(decay_scan_kernel<LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
+}
+
+// x: the packed projection; its q, k and v columns are prepared in place (T rows).
+extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act,
                                const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots,
                                const int* cu_q, const int* token_pos, float* out, int B, int* err, void* stream) {
-    if (B <= 0) return 0;
-    if (nh <= 0 || d <= 0 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
+    if (B <= 0 || T <= 0) return 0;
+    if (nh <= 0 || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
         return ILLM_ERR_BAD_ARG;
-    const long long smem = illm_decay_scan_smem(d, dv);
-    if (smem > 220 * 1024) return ILLM_ERR_BAD_ARG;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err};
-    illm_launch(decay_scan_kernel, dim3(B, nh), dim3(DS_THREADS), (size_t)smem, (cudaStream_t)stream, a);
+    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0};
+    a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (qk_act || v_act || rot || k_scale != 1.0f) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
+    if (d <= 32) decay_launch<1>(a, B, s);
+    else if (d <= 64) decay_launch<2>(a, B, s);
+    else if (d <= 128) decay_launch<4>(a, B, s);
+    else if (d <= 256) decay_launch<8>(a, B, s);
+    else if (d <= 512) decay_launch<16>(a, B, s);
+    else decay_launch<32>(a, B, s);
     return illm_launch_status();
 }
 

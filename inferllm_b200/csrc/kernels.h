@@ -10,6 +10,7 @@ extern "C" {
 
 // attention_decode.cu
 int illm_attention_decode(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_chunks, void* stream);
+int illm_attention_decode_ex(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_chunks, const float* sinks, const float* gate, int gate_stride, void* stream);
 int illm_attention_decode_merge(const float* part_acc, const float* part_ml, const int* token_pos, void* out, int T, int nh, int d, int n_chunks, int chunk_keys, int window, void* stream);
 int illm_attention_decode_supported(int d, int g, int page_size);
 int illm_attention_decode_static(const void* q, int q_stride, const void* kc, const void* vc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int max_len, char* err_msg, int err_len, void* stream);
@@ -32,8 +33,10 @@ int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc
 
 // decay_state.cu
 long long illm_decay_scan_smem(int d, int dv);
-int illm_decay_scan(const float* x, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, void* stream);
+int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, void* stream);
 int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
+
+int illm_attention_prefill_tc_ex(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, int* err, int wide_p, const float* sinks, const float* gate, int gate_stride, void* stream);
 
 // embedding.cu
 int illm_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H, int V, int* err, void* stream);

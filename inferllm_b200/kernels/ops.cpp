@@ -430,7 +430,7 @@ Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepVi
     return q;
 }
 
-bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }
+bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }      // head sizes up to 1024
 
 Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ctx, const StateView& st) {
     need(x, "the packed projection", true, DType::F32);
@@ -438,9 +438,9 @@ Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ct
         throw KernelError("decay_scan: the cache entry does not hold float32 state of heads x head size x value size");
     if (!decay_scan_supported(p.head_dim, p.v_head_dim))
         throw KernelError("decay_scan: a state of " + std::to_string(p.head_dim) + " x " + std::to_string(p.v_head_dim) +
-                          " per head does not fit a block's shared memory");
+                          " per head is beyond the kernel (head sizes up to 1024)");
     Mat out = new_mat_exact(dev, x.rows, (long long)p.n_heads * p.v_head_dim, DType::F32);
-    check_kernel(illm_decay_scan((const float*)x.p, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.head_dim, p.v_head_dim, p.qk_act, p.v_act,
+    check_kernel(illm_decay_scan((float*)x.p, (int)x.rows, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.head_dim, p.v_head_dim, p.qk_act, p.v_act,
                                  p.rot_dim ? p.cos_sin : nullptr, p.rot_dim, (int)p.n_pos, p.k_scale, p.decay, (float*)st.state, st.slots, ctx.cu_q,
                                  ctx.token_pos, (float*)out.p, ctx.B, ctx.err, dev.stream()),
                  "decay_scan");
@@ -541,15 +541,45 @@ Mat attention_prefill(Device& dev, const Mat& qkv, const KVView& kv, const StepV
     return out;
 }
 
-Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale) {
+Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
+                         const AttentionExtras* ex) {
     need(qkv, "qkv", true, DType::BF16);
     check_cache(kv, DType::BF16, g, "attention_prefill_tc");
     Mat out = new_mat(dev, qkv.rows, (long long)g.n_heads * g.head_dim, DType::BF16);
-    check_kernel(illm_attention_prefill_tc(qkv.p, (int)qkv.cols, (int)qkv.rows, kv.k, kv.v, kv.num_pages, kv.block_table, kv.width, ctx.cu_q,
-                                           ctx.seq_lens, out.p, ctx.B, ctx.max_q, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window,
-                                           scale, dev.tc_error_word(), dev.stream()),
+    check_kernel(illm_attention_prefill_tc_ex(qkv.p, (int)qkv.cols, (int)qkv.rows, kv.k, kv.v, kv.num_pages, kv.block_table, kv.width, ctx.cu_q,
+                                              ctx.seq_lens, out.p, ctx.B, ctx.max_q, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window,
+                                              scale, dev.tc_error_word(), ex && ex->wide_weights ? 1 : 0, ex ? ex->sinks : nullptr,
+                                              ex ? ex->gate : nullptr, ex ? ex->gate_stride : 0, dev.stream()),
                  "attention_prefill_tc");
     return out;
+}
+
+Mat attention_decode_ex(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale, long long max_len,
+                        const AttentionExtras& ex) {
+    need(qkv, "qkv", true, DType::BF16);
+    check_cache(kv, DType::BF16, g, "attention_decode");
+    const long long T = qkv.rows;
+    if (T > 65535) throw KernelError("attention_decode with sinks or gates takes at most 65535 tokens");
+    const int n_chunks = (int)std::max<long long>(1, ceil_div(max_len, kDecodeChunk));
+    float* part_acc = dev.alloc_n<float>((size_t)T * g.n_heads * n_chunks * g.head_dim);
+    float* part_ml = dev.alloc_n<float>((size_t)T * g.n_heads * n_chunks * 2);
+    Mat out = new_mat(dev, T, (long long)g.n_heads * g.head_dim, DType::BF16);
+    check_kernel(illm_attention_decode_ex(qkv.p, (int)qkv.cols, kv.k, kv.v, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, part_acc, part_ml,
+                                          out.p, (int)T, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, n_chunks, ex.sinks,
+                                          ex.gate, ex.gate_stride, dev.stream()),
+                 "attention_decode");
+    return out;
+}
+
+Mat attention_ex(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const AttentionExtras& ex) {
+    const int dv = kv.v_head_dim > 0 ? kv.v_head_dim : g.head_dim;
+    if (q.dtype == DType::BF16 && dv == g.head_dim) {
+        if (ctx.is_decode && attention_decode_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size))
+            return attention_decode_ex(dev, q, kv, ctx, g, scale, ctx.max_seq_len, ex);
+        if (!ctx.is_decode && attention_prefill_tc_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size))
+            return attention_prefill_tc(dev, q, kv, ctx, g, scale, &ex);
+    }
+    return attention_generic(dev, q, kv, ctx, g, scale, &ex);
 }
 
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale) {

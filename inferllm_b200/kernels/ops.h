@@ -148,6 +148,9 @@ struct AttentionExtras {
     const float* sinks = nullptr;
     const float* gate = nullptr;
     int gate_stride = 0;
+    // the tensor-core prompt kernel keeps sixteen bits of the softmax weights' mantissa (two bfloat16
+    // terms) instead of eight; the other kernels have float32 weights anyway
+    bool wide_weights = false;
 };
 Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
                       const AttentionExtras* extras = nullptr);
@@ -157,7 +160,14 @@ struct FusedRope { const float* cos_sin; int rot_dim; long long n_pos; bool writ
 Mat attention_decode_ring(Device& dev, const MatOrPartials& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
                           long long max_len, int splits /* 0: by policy */, const FusedRope* rope);
 Mat attention_prefill(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
-Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
+Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
+                         const AttentionExtras* extras = nullptr);
+// The split-key decode kernel on CUDA cores (float32 scores and weights) with sinks and gates in its merge.
+Mat attention_decode_ex(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale, long long max_len,
+                        const AttentionExtras& extras);
+// Attention with extras: the tensor-core prompt kernel and the split-key decode kernel where the
+// sizes allow (bfloat16, keys and values of one size, 64 or 128), the general kernel otherwise.
+Mat attention_ex(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const AttentionExtras& extras);
 // Attention of the step's tokens over a cache entry: picks the kernel for the dtype, head size and kind of step.
 Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
 
@@ -184,7 +194,8 @@ struct QkPrep {
 Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepView& ctx, const KVView& kv, DType act_dtype);
 
 // The decayed linear-attention recurrence over per-sequence state (csrc/decay_state.cu): x_f32 is the
-// packed float32 projection, state the cache entry's [slots, heads, d, dv] float32.  Returns float32
+// packed float32 projection (its q, k and v columns are prepared in place), state the cache entry's
+// float32 [slots, heads x d x dv] (the kernel's own layout).  Returns float32
 // [T, heads * dv].
 struct DecayScan {
     int q_off = 0, k_off = 0, v_off = 0;

@@ -465,7 +465,8 @@ struct Attention : Mixer {
             ex.gate = (const float*)x.p + (q_rows() + k_rows() + v_rows());
             ex.gate_stride = (int)x.cols;
         }
-        Mat o = ops::attention_generic(dev, q, kv, ctx, g, scale, &ex);
+        ex.wide_weights = true;       // the softmax weights are not to be rounded to eight bits
+        Mat o = ops::attention_ex(dev, q, kv, ctx, g, scale, ex);
         return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, false);
     }
 
