@@ -15,12 +15,13 @@
 //
 // decay_scan_kernel: the columns of S evolve independently of one another (S[:, j] only ever meets
 // v[j]), so a block owns one (sequence, head, group of columns) and a thread keeps its part of the
-// state in registers for the whole step: 32 rows of one column, the rows of a column dealt to LI
-// neighbouring lanes (LI = d / 32 rounded up to a power of two, rows beyond d are zeros).  The step's
+// state in registers for the whole step: R rows of C columns (R C = 32; four rows of eight columns up
+// to head size 128, so that a token costs a thread few shared-memory reads per FMA), the rows of a
+// column group dealt to LI neighbouring lanes (R LI >= d, rows beyond d are zeros).  The step's
 // tokens come in tiles through two shared-memory buffers filled by cp.async, the next tile on its
 // way while this one is used; every thread runs a tile's tokens one after the other without any
-// synchronisation: 32 independent chains s = decay s + k v[j], its part of o_t[j] = sum_i s q[i], and
-// a fixed tree of shuffles over the LI lanes of the column.  What bounds it is the float32 FMA rate
+// synchronisation: 32 independent chains s = decay s + k v[j], its parts of o_t[j] = sum_i s q[i], and
+// a fixed tree of shuffles over the LI lanes of the column group.  What bounds it is the float32 FMA rate
 // and the latency of the chain, not memory; a prompt of one sequence fills heads x dv / (128 / LI)
 // blocks.  The state is stored column by column ([slots, heads, dv, d]), so that a thread's rows are
 // 16-byte pieces.
@@ -31,10 +32,13 @@
 // group_norm_gate_kernel: what follows the recurrence in such mixers: an RMS norm over groups of the
 // concatenated heads (one group = all heads together, with a weight; or one group per head, without),
 // times an activation of a gate projection (sigmoid or silu), rounded once to the activation dtype.
+#include <type_traits>
+
 #include "common.cuh"
 
 #define DS_THREADS 128
 #define DS_MAX_TILE 16
+#define DS_U 4             // tokens whose reductions are interleaved
 
 struct DecayScanArgs {
     float* x;
@@ -51,12 +55,19 @@ struct DecayScanArgs {
     int* err;
     int tile;                       // tokens staged at a time
     int vec;                        // 16-byte copies are possible
+    int inline_prep;                // the scan prepares q, k, v itself while it stages them (steps of few tokens)
 };
 
 __device__ __forceinline__ float act_of(float v, int act) {
     if (act == 1) return v / (1.0f + expf(-v));
     if (act == 2) return 1.0f / (1.0f + expf(-v));
     return v;
+}
+
+// One channel of a rotated pair: own * cos -+ other * sin, each operation rounded by itself, so that the
+// preparation kernel and the scan's own staging give the same bits.
+__device__ __forceinline__ float rot_val(float own, float other, float cs, float sn, bool lower) {
+    return lower ? __fsub_rn(__fmul_rn(own, cs), __fmul_rn(other, sn)) : __fadd_rn(__fmul_rn(own, cs), __fmul_rn(other, sn));
 }
 
 __global__ void __launch_bounds__(128) decay_prep_kernel(DecayScanArgs a) {
@@ -76,10 +87,10 @@ __global__ void __launch_bounds__(128) decay_prep_kernel(DecayScanArgs a) {
             const float cs = a.cos_sin[((size_t)p * half + c) * 2], sn = a.cos_sin[((size_t)p * half + c) * 2 + 1];
             const float q1 = act_of(q[c], a.qk_act), q2 = act_of(q[c + half], a.qk_act);
             const float k1 = act_of(k[c], a.qk_act), k2 = act_of(k[c + half], a.qk_act);
-            q[c] = q1 * cs - q2 * sn;
-            q[c + half] = q2 * cs + q1 * sn;
-            k[c] = (k1 * cs - k2 * sn) * a.k_scale;
-            k[c + half] = (k2 * cs + k1 * sn) * a.k_scale;
+            q[c] = rot_val(q1, q2, cs, sn, true);
+            q[c + half] = rot_val(q2, q1, cs, sn, false);
+            k[c] = rot_val(k1, k2, cs, sn, true) * a.k_scale;
+            k[c + half] = rot_val(k2, k1, cs, sn, false) * a.k_scale;
         } else if (c >= a.rot) {
             q[c] = act_of(q[c], a.qk_act);
             k[c] = act_of(k[c], a.qk_act) * a.k_scale;
@@ -96,35 +107,41 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int LI>
+// R rows x C columns of the state per thread (R C = 32), the rows of a column group over LI lanes.
+template <int R, int LI>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float sm[];
-    constexpr int JW = 32 / LI;                     // columns per warp
+    constexpr int C = 32 / R;                       // columns per thread
+    constexpr int M = R / 4;                        // 16-byte pieces of q and k per thread
+    constexpr int JW = C * (32 / LI);               // columns per warp
     constexpr int JB = JW * (DS_THREADS / 32);      // columns per block
-    constexpr int DP = 32 * LI;                     // rows with padding
+    constexpr int DP = R * LI;                      // rows with padding
     constexpr int ROW = 2 * DP + JB;                // floats of one staged token: q, k, v
     const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * JB;
     const int d = a.d, dv = a.dv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane % LI, jl = warp * JW + lane / LI;
-    const int j = j0 + jl;
-    const bool col_ok = j < dv;
+    const int g = lane % LI;
+    const int jl = (warp * (32 / LI) + lane / LI) * C;      // first of this thread's columns within the block
     const int jn = dv - j0 < JB ? dv - j0 : JB;     // columns of this block that exist
     const float dec = a.decay[h];
-    float* Sg = a.state + ((size_t)a.slots[b] * a.nh + h) * (size_t)d * dv + (size_t)j * d;       // this thread's column
-    // row of register (m, c): m * 4 LI + 4 g + c, so that the LI lanes of a column read 16-byte pieces
-    // of q, k and the state that lie side by side
-    float s[8][4];
+    float* Sg = a.state + ((size_t)a.slots[b] * a.nh + h) * (size_t)d * dv;       // [dv][d]
+    // row of register (m, r): m * 4 LI + 4 g + r, so that the LI lanes of a column group read 16-byte
+    // pieces of q, k and the state that lie side by side
+    float s[C][M][4];
 #pragma unroll
-    for (int m = 0; m < 8; m++) {
-        const int i = m * 4 * LI + 4 * g;
-        if (a.vec && col_ok && i < d) {
-            const float4 v4 = *reinterpret_cast<const float4*>(Sg + i);
-            s[m][0] = v4.x; s[m][1] = v4.y; s[m][2] = v4.z; s[m][3] = v4.w;
-        } else {
+    for (int c = 0; c < C; c++) {
+        const int j = j0 + jl + c;
 #pragma unroll
-            for (int c = 0; c < 4; c++) s[m][c] = (col_ok && i + c < d) ? Sg[i + c] : 0.f;
+        for (int m = 0; m < M; m++) {
+            const int i = m * 4 * LI + 4 * g;
+            if (a.vec && j < dv && i < d) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Sg + (size_t)j * d + i);
+                s[c][m][0] = v4.x; s[c][m][1] = v4.y; s[c][m][2] = v4.z; s[c][m][3] = v4.w;
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; r++) s[c][m][r] = (j < dv && i + r < d) ? Sg[(size_t)j * d + i + r] : 0.f;
+            }
         }
     }
     // rows beyond d and columns beyond dv stay zero in both buffers
@@ -134,7 +151,35 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     auto stage = [&](int buf, int tb) {
         const int n = t1 - tb < a.tile ? t1 - tb : a.tile;
         float* base = sm + buf * a.tile * ROW;
-        if (a.vec) {
+        if (a.inline_prep) {
+            const int per = 2 * d + jn, half = a.rot >> 1;
+            for (int idx = threadIdx.x; idx < n * per; idx += DS_THREADS) {
+                const int tt = idx / per, c = idx - tt * per;
+                const float* row = a.x + (size_t)(tb + tt) * a.ld;
+                float* dst = base + tt * ROW;
+                if (c < 2 * d) {
+                    const bool is_k = c >= d;
+                    const int e = is_k ? c - d : c;
+                    const float* src = row + (is_k ? a.k_off : a.q_off) + h * d;
+                    float val = act_of(src[e], a.qk_act);
+                    if (e < a.rot) {
+                        int p = a.token_pos[tb + tt];
+                        if (p < 0 || p >= a.n_pos) {
+                            atomicExch(a.err, 3);
+                            p = 0;
+                        }
+                        const bool lower = e < half;
+                        const int jp = lower ? e : e - half;
+                        const float cs = a.cos_sin[((size_t)p * half + jp) * 2], sn = a.cos_sin[((size_t)p * half + jp) * 2 + 1];
+                        const float other = act_of(src[lower ? e + half : e - half], a.qk_act);
+                        val = rot_val(val, other, cs, sn, lower);
+                    }
+                    dst[(is_k ? DP : 0) + e] = is_k ? val * a.k_scale : val;
+                } else {
+                    dst[2 * DP + c - 2 * d] = act_of(row[a.v_off + h * dv + j0 + c - 2 * d], a.v_act);
+                }
+            }
+        } else if (a.vec) {
             const int cq = d >> 2, cv = jn >> 2, per = 2 * cq + cv;
             for (int idx = threadIdx.x; idx < n * per; idx += DS_THREADS) {
                 const int tt = idx / per, c = idx - tt * per;
@@ -157,6 +202,75 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    auto tokens = [&](auto group, const float* rowp, int t) {
+        constexpr int U = decltype(group)::value;
+        float p[U][C];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const float4* q4 = reinterpret_cast<const float4*>(rowp + u * ROW) + g;
+            const float4* k4 = reinterpret_cast<const float4*>(rowp + u * ROW + DP) + g;
+            const float* vp = rowp + u * ROW + 2 * DP + jl;
+            float v[C];
+#pragma unroll
+            for (int c = 0; c < C; c++) {
+                v[c] = vp[c];
+                p[u][c] = 0.f;
+            }
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float4 kk = k4[m * LI], qq = q4[m * LI];
+#pragma unroll
+                for (int c = 0; c < C; c++) {
+                    s[c][m][0] = fmaf(dec, s[c][m][0], kk.x * v[c]);
+                    s[c][m][1] = fmaf(dec, s[c][m][1], kk.y * v[c]);
+                    s[c][m][2] = fmaf(dec, s[c][m][2], kk.z * v[c]);
+                    s[c][m][3] = fmaf(dec, s[c][m][3], kk.w * v[c]);
+                    p[u][c] = fmaf(s[c][m][0], qq.x, p[u][c]);
+                    p[u][c] = fmaf(s[c][m][1], qq.y, p[u][c]);
+                    p[u][c] = fmaf(s[c][m][2], qq.z, p[u][c]);
+                    p[u][c] = fmaf(s[c][m][3], qq.w, p[u][c]);
+                }
+            }
+        }
+        // the sums over the LI lanes of the column group, a fixed tree: while a lane holds several
+        // columns, each step halves them (a lane keeps the lower half if its bit is clear and gets the
+        // partner's part of that half); with one column left the steps are plain
+        int first = 0;          // first column this lane still holds
+        int nc = C, plain_bits = 0;
+#pragma unroll
+        for (int o = LI / 2; o >= 1; o >>= 1) {
+            const bool up = (lane & o) != 0;
+            if (nc > 1) {
+                const int hf = nc / 2;
+#pragma unroll
+                for (int u = 0; u < U; u++)
+#pragma unroll
+                    for (int c = 0; c < C / 2; c++) {
+                        if (c < hf) {
+                            const float mine = up ? p[u][c + hf] : p[u][c];
+                            const float theirs = up ? p[u][c] : p[u][c + hf];
+                            p[u][c] = mine + __shfl_xor_sync(0xffffffffu, theirs, o);
+                        }
+                    }
+                if (up) first += hf;
+                nc = hf;
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; u++) p[u][0] += __shfl_xor_sync(0xffffffffu, p[u][0], o);
+                plain_bits |= o;
+            }
+        }
+        // lanes that differ only in the bits of the plain steps hold the same sum: one of them writes
+        if ((lane & plain_bits) == 0) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                float* orow = a.out + (size_t)(t + u) * a.nh * dv + (size_t)h * dv + j0 + jl + first;
+#pragma unroll
+                for (int c = 0; c < C; c++)
+                    if (c < nc && j0 + jl + first + c < dv) orow[c] = p[u][c];
+            }
+        }
+    };
     if (t0 < t1) stage(0, t0);
     int buf = 0;
     for (int tb = t0; tb < t1; tb += a.tile, buf ^= 1) {
@@ -169,39 +283,27 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
         }
         __syncthreads();
         const float* base = sm + buf * a.tile * ROW;
-        for (int tt = 0; tt < n; tt++) {
-            const float4* q4 = reinterpret_cast<const float4*>(base + tt * ROW) + g;
-            const float4* k4 = reinterpret_cast<const float4*>(base + tt * ROW + DP) + g;
-            const float vj = base[tt * ROW + 2 * DP + jl];
-            float part0 = 0.f, part1 = 0.f;
-#pragma unroll
-            for (int m = 0; m < 8; m++) {
-                const float4 kk = k4[m * LI], qq = q4[m * LI];
-                s[m][0] = fmaf(dec, s[m][0], kk.x * vj);
-                s[m][1] = fmaf(dec, s[m][1], kk.y * vj);
-                s[m][2] = fmaf(dec, s[m][2], kk.z * vj);
-                s[m][3] = fmaf(dec, s[m][3], kk.w * vj);
-                part0 = fmaf(s[m][0], qq.x, part0);
-                part1 = fmaf(s[m][1], qq.y, part1);
-                part0 = fmaf(s[m][2], qq.z, part0);
-                part1 = fmaf(s[m][3], qq.w, part1);
-            }
-            float part = part0 + part1;
-#pragma unroll
-            for (int o = 1; o < LI; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (g == 0 && col_ok) a.out[(size_t)(tb + tt) * a.nh * dv + (size_t)h * dv + j] = part;
-        }
+        // tokens in groups of DS_U: the state chains run through the group's tokens in order, and the
+        // group's reductions go level by level side by side, so that one token's shuffle latency is
+        // spent on the others' shuffles
+        int tt = 0;
+        for (; tt + DS_U <= n; tt += DS_U) tokens(std::integral_constant<int, DS_U>(), base + tt * ROW, tb + tt);
+        for (; tt < n; tt++) tokens(std::integral_constant<int, 1>(), base + tt * ROW, tb + tt);
         __syncthreads();        // the buffer is filled again by the tile after the next
     }
 #pragma unroll
-    for (int m = 0; m < 8; m++) {
-        const int i = m * 4 * LI + 4 * g;
-        if (a.vec && col_ok && i < d) {
-            *reinterpret_cast<float4*>(Sg + i) = make_float4(s[m][0], s[m][1], s[m][2], s[m][3]);
-        } else {
+    for (int c = 0; c < C; c++) {
+        const int j = j0 + jl + c;
 #pragma unroll
-            for (int c = 0; c < 4; c++)
-                if (col_ok && i + c < d) Sg[i + c] = s[m][c];
+        for (int m = 0; m < M; m++) {
+            const int i = m * 4 * LI + 4 * g;
+            if (a.vec && j < dv && i < d) {
+                *reinterpret_cast<float4*>(Sg + (size_t)j * d + i) = make_float4(s[c][m][0], s[c][m][1], s[c][m][2], s[c][m][3]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+                    if (j < dv && i + r < d) Sg[(size_t)j * d + i + r] = s[c][m][r];
+            }
         }
     }
 }
@@ -212,14 +314,14 @@ extern "C" long long illm_decay_scan_smem(int d, int dv) {
     return d <= 1024 ? 40 * 1024 : (1LL << 40);
 }
 
-template <int LI>
+template <int R, int LI>
 static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
-    constexpr int DP = 32 * LI, JB = (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
+    constexpr int DP = R * LI, JB = (32 / R) * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
     int tile = (int)(40 * 1024 / sizeof(float) / (2 * ROW));
     a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    illm_launch(decay_scan_kernel<LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<R, LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    illm_launch(decay_scan_kernel<R, LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
 }
 
 // x: the packed projection; its q, k and v columns are prepared in place (T rows).
@@ -229,16 +331,22 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     if (B <= 0 || T <= 0) return 0;
     if (nh <= 0 || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
         return ILLM_ERR_BAD_ARG;
-    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0};
+    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0};
     a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15);
     cudaStream_t s = (cudaStream_t)stream;
-    if (qk_act || v_act || rot || k_scale != 1.0f) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
-    if (d <= 32) decay_launch<1>(a, B, s);
-    else if (d <= 64) decay_launch<2>(a, B, s);
-    else if (d <= 128) decay_launch<4>(a, B, s);
-    else if (d <= 256) decay_launch<8>(a, B, s);
-    else if (d <= 512) decay_launch<16>(a, B, s);
-    else decay_launch<32>(a, B, s);
+    // a step of few tokens (single tokens of a batch) is not worth a launch of its own for the preparation
+    a.inline_prep = T <= 64 ? 1 : 0;
+    if (!a.inline_prep && (qk_act || v_act || rot || k_scale != 1.0f)) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
+    // four rows x eight columns per thread up to head size 128 (fewest shared-memory reads per FMA); more rows beyond
+    if (d <= 4) decay_launch<4, 1>(a, B, s);
+    else if (d <= 8) decay_launch<4, 2>(a, B, s);
+    else if (d <= 16) decay_launch<4, 4>(a, B, s);
+    else if (d <= 32) decay_launch<4, 8>(a, B, s);
+    else if (d <= 64) decay_launch<4, 16>(a, B, s);
+    else if (d <= 128) decay_launch<4, 32>(a, B, s);
+    else if (d <= 256) decay_launch<8, 32>(a, B, s);
+    else if (d <= 512) decay_launch<16, 32>(a, B, s);
+    else decay_launch<32, 32>(a, B, s);
     return illm_launch_status();
 }
 

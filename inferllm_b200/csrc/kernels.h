@@ -56,7 +56,7 @@ int illm_splitk_reduce(const float* ws, void* out, int out_dtype, long long n, i
 int illm_gemm_bf16_tc2(const void* X, const void* W, void* out, int out_dtype, int epi, int M, int N, int K, int* err, void* stream);
 
 // postnorm.cu
-int illm_scale_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* w, void* y, int y_dtype, int n_rows, int H, float alpha, float eps, void* stream);
+int illm_scale_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* w, void* y, int y_dtype, int n_rows, int H, float alpha, float eps, const float* partials, int splits, long long split_stride, void* stream);
 
 // qk_prep.cu
 int illm_qk_prep(const void* x, int x_dtype, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int d, int dv, const float* bq, const float* bk, const float* bv, const float* wq, const float* wk, float eps, const float* cos_sin, int rot, int pairs, int n_pos, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* q_out, void* kc, void* vc, int act_dtype, int T, int* err, void* stream);

@@ -395,20 +395,21 @@ Mat attention_generic(Device& dev, const Mat& qkv, const KVView& kv, const StepV
 
 // ---- pieces of mixers other than the plain attention
 
-Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const Mat* delta, const Mat& w, float alpha, float eps, DType out_dtype) {
+Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const MatOrPartials* delta, const Mat& w, float alpha, float eps, DType out_dtype) {
     need(resid, "resid", true, DType::F32);
     need(w, "norm weight", true, DType::F32);
     const long long H = resid.cols;
     if (w.rows * w.cols != H)
         throw KernelError("norm weight has " + std::to_string(w.rows * w.cols) + " elements, the rows have " + std::to_string(H));
-    if (delta) {
-        need(*delta, "delta");
-        if (delta->rows != resid.rows || delta->cols != H) throw KernelError("scale_add_rmsnorm: delta does not match the stream");
-    }
+    const Partials* part = delta && delta->is_partials() ? &delta->part : nullptr;
+    const Mat* d = delta && !delta->is_partials() ? &delta->m : nullptr;
+    if (d) need(*d, "delta");
+    if ((d && (d->rows != resid.rows || d->cols != H)) || (part && (part->rows != resid.rows || part->cols != H)))
+        throw KernelError("scale_add_rmsnorm: delta does not match the stream");
     Mat y = new_mat(dev, resid.rows, H, out_dtype);
-    check_kernel(illm_scale_add_rmsnorm((float*)resid.p, delta ? delta->p : nullptr, delta ? code_of(delta->dtype, "scale_add_rmsnorm") : 0,
-                                        (const float*)w.p, y.p, code_of(out_dtype, "scale_add_rmsnorm"), (int)resid.rows, (int)H, alpha, eps,
-                                        dev.stream()),
+    check_kernel(illm_scale_add_rmsnorm((float*)resid.p, d ? d->p : nullptr, d ? code_of(d->dtype, "scale_add_rmsnorm") : 0, (const float*)w.p, y.p,
+                                        code_of(out_dtype, "scale_add_rmsnorm"), (int)resid.rows, (int)H, alpha, eps, part ? part->ws : nullptr,
+                                        part ? part->splits : 0, part ? part->rows * part->cols : 0, dev.stream()),
                  "scale_add_rmsnorm");
     return y;
 }

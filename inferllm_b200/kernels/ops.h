@@ -175,7 +175,7 @@ Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx
 
 // stream.x <- rmsnorm(alpha * stream.x + delta) * w (w float32, the stream float32); returns the new rows
 // in `out_dtype` as well (what the next sublayer reads).
-Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const Mat* delta, const Mat& weight_f32, float alpha, float eps, DType out_dtype);
+Mat scale_add_rmsnorm(Device& dev, const Mat& resid, const MatOrPartials* delta, const Mat& weight_f32, float alpha, float eps, DType out_dtype);
 
 // Between the packed projection x [T, ld] (float32 or the activation dtype) of an attention layer and its attention kernel:
 // optional biases, optional RMS norms over a token's whole q and whole k projection, rotation of the

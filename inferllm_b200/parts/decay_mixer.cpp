@@ -100,7 +100,7 @@ struct DecayLinearAttention : Mixer {
         check_cuda(cudaMemcpy(decay_buf.get(), decay.data(), decay.size() * sizeof(float), cudaMemcpyHostToDevice), "uploading the decays");
     }
 
-    MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool) override {
+    MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool may_defer) override {
         if (cache.kind != CacheView::State) throw EngineError("decay_linear_attention: the layer's cache entry holds no state");
         if (!writes) throw EngineError("decay_linear_attention: the state belongs to one layer");
         Device& dev = *rt->dev;
@@ -128,7 +128,7 @@ struct DecayLinearAttention : Mixer {
         const float* gate = (const float*)x.p + (2 * qk_rows() + v_rows());
         Mat y = ops::group_norm_gate(dev, o, joint_norm ? (int)v_rows() : v_head_dim, joint_norm ? (const float*)norm_w.m.p : nullptr, norm_eps,
                                      gate, (int)x.cols, gate_act, rt->dtype);
-        return ops::linear(dev, rt->gemm, y, w_o, out_f32 ? DType::F32 : rt->dtype, false);
+        return ops::linear(dev, rt->gemm, y, w_o, out_f32 ? DType::F32 : rt->dtype, may_defer);
     }
 };
 

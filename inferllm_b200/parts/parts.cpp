@@ -203,13 +203,8 @@ struct RMSNorm : Norm {
     }
     Mat forward_into_stream(ResidualStream& stream) override {
         if (weight.m.dtype != DType::F32) throw EngineError("rmsnorm: the norm after the sum needs its weight in float32 (float32_weight)");
-        Mat delta;
-        const Mat* d = nullptr;
-        if (stream.has_pending) {
-            delta = stream.pending.is_partials() ? ops::materialize(*rt->dev, stream.pending.part, rt->dtype) : stream.pending.m;
-            d = &delta;
-            stream.has_pending = false;
-        }
+        const MatOrPartials* d = stream.has_pending ? &stream.pending : nullptr;      // unreduced slices are added up by the kernel
+        stream.has_pending = false;
         return ops::scale_add_rmsnorm(*rt->dev, stream.x, d, weight.m, residual_scale, eps, rt->dtype);
     }
     Mat forward(ResidualStream& stream, const int* rows, long long n_rows) override {
@@ -429,7 +424,7 @@ struct Attention : Mixer {
         return own_kv ? CacheRequest::paged(n_kv_heads, head_dim, window, v_head_dim) : CacheRequest();
     }
 
-    MatOrPartials forward_general(const Mat& h, const StepContext& ctx, KVView kv) {
+    MatOrPartials forward_general(const Mat& h, const StepContext& ctx, KVView kv, bool may_defer) {
         Device& dev = *rt->dev;
         const ops::Geometry g{n_heads, n_kv_heads, head_dim};
         if (kv.n_kv_heads != n_kv_heads || kv.head_dim != head_dim || (kv.v_head_dim > 0 ? kv.v_head_dim : kv.head_dim) != v_head_dim)
@@ -467,7 +462,7 @@ struct Attention : Mixer {
         }
         ex.wide_weights = true;       // the softmax weights are not to be rounded to eight bits
         Mat o = ops::attention_ex(dev, q, kv, ctx, g, scale, ex);
-        return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, false);
+        return ops::linear(dev, rt->gemm, o, w_o, out_f32 ? DType::F32 : rt->dtype, may_defer);
     }
 
     MatOrPartials forward(const Mat& h, const StepContext& ctx, const CacheView& cache, bool writes, bool may_defer) override {
@@ -475,7 +470,7 @@ struct Attention : Mixer {
         Device& dev = *rt->dev;
         KVView kv = cache.kv;
         kv.writes = writes;
-        if (general()) return forward_general(h, ctx, kv);
+        if (general()) return forward_general(h, ctx, kv, may_defer);
         const ops::Geometry g{n_heads, n_kv_heads, head_dim};
         const float* table = nullptr;
         int rot = 0;
@@ -539,7 +534,7 @@ struct GatedMLP : FeedForward {
     MatOrPartials forward(const Mat& h, const StepContext&, bool may_defer) override {
         Device& dev = *rt->dev;
         return ops::linear(dev, rt->gemm, ops::linear_gated(dev, rt->gemm, h, w_gate_up), w_down, out_f32 ? DType::F32 : rt->dtype,
-                           may_defer && !out_f32);
+                           may_defer);
     }
 };
 
@@ -615,10 +610,11 @@ struct PostNormBlock : Block {
             stream.flush();
             stream.h = ops::cast(*stream.dev, stream.x, ctx.rt->dtype);
         }
-        stream.add(mixer->forward(stream.h, ctx, cache, writes, false));
+        // the outputs only go into the norm's sum, so they may stay unreduced K slices
+        stream.add(mixer->forward(stream.h, ctx, cache, writes, true));
         stream.h = norms.at("norm1")->forward_into_stream(stream);
         if (!ffn) return;
-        stream.add(ffn->forward(stream.h, ctx, false));
+        stream.add(ffn->forward(stream.h, ctx, true));
         stream.h = norms.at("norm2")->forward_into_stream(stream);
     }
 };
