@@ -192,7 +192,7 @@ def run_design(args):
     from torch.profiler import ProfilerActivity, profile
 
     from inferllm_b200 import Engine, EngineOptions, StepItem, config_from_dict
-    T, B, C = args.design_tokens, args.batch, args.design_context
+    T, B, C, NP = args.design_tokens, args.batch, args.design_context, args.design_prompts
     K, W = args.steps, max(3, args.warmup)
     g = torch.Generator().manual_seed(0)
 
@@ -207,6 +207,8 @@ def run_design(args):
         return e0.elapsed_time(e1) / n
 
     def by_kernel(fn):
+        if args.design_no_kernel_times:
+            return {}
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
             fn()
             torch.cuda.synchronize()
@@ -220,14 +222,15 @@ def run_design(args):
     for size in args.design_size.split(","):
         z = DESIGN_SIZES[size]
         for which, cfgd in (("vokelix", vokelix_config(z)), ("llama", llama_twin(z))):
-            eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=B * (C + 64) + T + 64, max_seq_len=4096,
-                                                                           max_batch=max(B, 8)), seed=0)
+            eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=max(B * (C + 64), NP * (T + 64)) + 64,
+                                                                           max_seq_len=4096, max_batch=max(B, NP, 8)), seed=0)
             ids = torch.randint(0, 32000, (T,), generator=g).tolist()
 
             def prefill():
-                s = eng.new_sequence()
-                eng.step([StepItem(s, ids, [T - 1])])
-                eng.end_sequence(s)
+                ss = [eng.new_sequence() for _ in range(NP)]
+                eng.step([StepItem(s, ids, [T - 1]) for s in ss])
+                for s in ss:
+                    eng.end_sequence(s)
 
             for _ in range(3):
                 prefill()
@@ -248,7 +251,7 @@ def run_design(args):
             for s in slots:
                 eng.end_sequence(s)
             print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else len(DESIGN_LAYERS),
-                              "prefill_tokens": T, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(T / pf_ms * 1e3, 1),
+                              "prefill_tokens": T, "prefill_prompts": NP, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(NP * T / pf_ms * 1e3, 1),
                               "decode_batch": B, "decode_context": C, "decode_ms": round(dec_ms, 4),
                               "decode_tok_s": round(B / dec_ms * 1e3, 1), "prefill_kernels_us": pf_kernels,
                               "decode_kernels_us": dec_kernels}), flush=True)
@@ -485,6 +488,9 @@ def main():
     ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")
     ap.add_argument("--design-context", type=int, default=2048, help="with --design: position at which the timed decode steps end")
+    ap.add_argument("--design-prompts", type=int, default=1, help="with --design: prompts of --design-tokens tokens each in the prompt step")
+    ap.add_argument("--design-no-kernel-times", action="store_true", help="with --design: leave out the time per kernel (it uses the "
+                    "driver's activity records, which a profiler around the program wants for itself)")
     args = ap.parse_args()
 
     if args.design:

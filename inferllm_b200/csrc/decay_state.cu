@@ -38,6 +38,9 @@
 
 #define DS_THREADS 128
 #define DS_MAX_TILE 16
+#ifndef DS_C128
+#define DS_C128 4          // columns per thread at head sizes 65..128
+#endif
 #define DS_U 4             // tokens whose reductions are interleaved
 
 struct DecayScanArgs {
@@ -107,12 +110,11 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-// R rows x C columns of the state per thread (R C = 32), the rows of a column group over LI lanes.
-template <int R, int LI>
+// R rows x C columns of the state per thread, the rows of a column group over LI lanes.
+template <int R, int C, int LI>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float sm[];
-    constexpr int C = 32 / R;                       // columns per thread
     constexpr int M = R / 4;                        // 16-byte pieces of q and k per thread
     constexpr int JW = C * (32 / LI);               // columns per warp
     constexpr int JB = JW * (DS_THREADS / 32);      // columns per block
@@ -314,14 +316,14 @@ extern "C" long long illm_decay_scan_smem(int d, int dv) {
     return d <= 1024 ? 40 * 1024 : (1LL << 40);
 }
 
-template <int R, int LI>
+template <int R, int C, int LI>
 static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
-    constexpr int DP = R * LI, JB = (32 / R) * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
+    constexpr int DP = R * LI, JB = C * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
     int tile = (int)(40 * 1024 / sizeof(float) / (2 * ROW));
     a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<R, LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    illm_launch(decay_scan_kernel<R, LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<R, C, LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    illm_launch(decay_scan_kernel<R, C, LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
 }
 
 // x: the packed projection; its q, k and v columns are prepared in place (T rows).
@@ -338,15 +340,15 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     a.inline_prep = T <= 64 ? 1 : 0;
     if (!a.inline_prep && (qk_act || v_act || rot || k_scale != 1.0f)) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
     // four rows x eight columns per thread up to head size 128 (fewest shared-memory reads per FMA); more rows beyond
-    if (d <= 4) decay_launch<4, 1>(a, B, s);
-    else if (d <= 8) decay_launch<4, 2>(a, B, s);
-    else if (d <= 16) decay_launch<4, 4>(a, B, s);
-    else if (d <= 32) decay_launch<4, 8>(a, B, s);
-    else if (d <= 64) decay_launch<4, 16>(a, B, s);
-    else if (d <= 128) decay_launch<4, 32>(a, B, s);
-    else if (d <= 256) decay_launch<8, 32>(a, B, s);
-    else if (d <= 512) decay_launch<16, 32>(a, B, s);
-    else decay_launch<32, 32>(a, B, s);
+    if (d <= 4) decay_launch<4, 8, 1>(a, B, s);
+    else if (d <= 8) decay_launch<4, 8, 2>(a, B, s);
+    else if (d <= 16) decay_launch<4, 8, 4>(a, B, s);
+    else if (d <= 32) decay_launch<4, 8, 8>(a, B, s);
+    else if (d <= 64) decay_launch<4, 8, 16>(a, B, s);
+    else if (d <= 128) decay_launch<4, DS_C128, 32>(a, B, s);
+    else if (d <= 256) decay_launch<8, 4, 32>(a, B, s);
+    else if (d <= 512) decay_launch<16, 2, 32>(a, B, s);
+    else decay_launch<32, 1, 32>(a, B, s);
     return illm_launch_status();
 }
 

@@ -66,6 +66,8 @@ Engine::Engine(std::unique_ptr<ArchConfig> config, const EngineOptions& options)
     std::set<std::string> said;
     for (const LayerSpec& ls : spec.layers) {
         if (ls.mixer.kind != "attention" || !ls.mixer.has("n_heads")) continue;
+        // a layer with sinks, gates, biases or norms of its own takes the general path (ops::attention_ex), which this line does not describe
+        if (ls.mixer.get_bool("sink", false) || ls.mixer.get_bool("qkv_bias", false) || ls.mixer.has("out_gate") || ls.mixer.has("qk_norm")) continue;
         const int nh = (int)ls.mixer.get_int("n_heads"), nkv = (int)ls.mixer.get_int("n_kv_heads", nh), d = (int)ls.mixer.get_int("head_dim", 0);
         const std::string what = ops::attention_kernels_for(dtype, nh, nkv, d, options.page_size);
         const std::string line = std::to_string(nh) + " heads over " + std::to_string(nkv) + " of size " + std::to_string(d) + ", pages of " +

@@ -145,10 +145,9 @@ static int run(int argc, char** argv) {
             if (line.find_first_not_of(" \t\r\n") != std::string::npos) prompts.push_back(ids_of(line));
     }
     if (!random_prompts.empty()) {
-        long long vocab = 0;
-        if (cfg) vocab = cfg_json.at("vocab_size").as_int();
-        else vocab = read_config_json(model_dir).at("vocab_size").as_int();
-        if (vocab <= 0) throw ConfigError("config.json: vocab_size must be positive");
+        // the vocabulary's size as the architecture's configuration class reads it (the key differs between architectures)
+        const long long vocab = (cfg ? cfg->model_spec() : config_from_folder(model_dir)->model_spec()).vocab_size;
+        if (vocab <= 0) throw ConfigError("config.json: the vocabulary's size must be positive");
         std::mt19937_64 rng(seed >= 0 ? (unsigned long long)seed : std::random_device{}());
         for (int n : ids_of(random_prompts)) {
             std::vector<int> p;
@@ -179,7 +178,8 @@ static int run(int argc, char** argv) {
         fprintf(stderr, "llama: give -m DIR, or --config FILE with --random-weights SEED\n");
         return 2;
     }
-    const int end_token = model.has_end_token() ? model.end_token() : 2;
+    // a configuration that names no end token: nothing but the length ends a request
+    const int end_token = model.has_end_token() ? model.end_token() : -1;
     model.init((unsigned)top_k, top_p, temp, repeat_penalty, repeat_last_n, seed, end_token);
     const std::vector<int> none;
     GenerationResult res = model.generate(prompts, n_predict, no_stop ? &none : nullptr);
