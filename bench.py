@@ -143,7 +143,7 @@ def prefill_flops(cfg, n_layers, T, fig):
     return linear + attn
 
 
-# ---- beside the contract: the Vokelix design next to LLaMA layers of equal size (--design vokelix)
+# ---- beside the default workload: the Vokelix design next to LLaMA layers of equal size (--design vokelix)
 
 DESIGN_SIZES = {          # width, feed-forward, heads, kv heads, head size (keys and values), heads of the linear layers
     "1k": dict(width=1024, ff=2816, heads=8, kv=2, d=128, lin_heads=8, lin_d=128),
@@ -483,7 +483,7 @@ def main():
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
                     "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
-    ap.add_argument("--design", choices=["vokelix"], help="beside the contract: prompt and decode throughput of this design "
+    ap.add_argument("--design", choices=["vokelix"], help="beside the default workload: prompt and decode throughput of this design "
                     "at a few layer sizes, each next to LLaMA layers of equal size, with the time per kernel")
     ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")
