@@ -145,14 +145,41 @@ __device__ __forceinline__ void rd_encoded_chunk(const RdRope& rp, const bf16* _
     }
 }
 
-template <int D, bool FUSE>
+// What mixers beyond the plain attention add: `sinks` (float32 [nh]: one more term exp(sink) of the
+// softmax denominator, without a value), `gate` (float32, gate[t * gate_stride + h]: the head's output
+// is multiplied by its sigmoid).  WIDE: the softmax weights enter the product with V as two bfloat16
+// terms (P1 = P rounded, P2 = P - P1 rounded), sixteen bits of their mantissa instead of eight.
+struct RdExtras {
+    const float* sinks;
+    const float* gate;
+    int gate_stride;
+};
+
+// num / den of a head with the sink's term added (m and the sink in units of log2) and the gate applied
+__device__ __forceinline__ float rd_finish(float num, float den, float m, const RdExtras& ex, int t, int h) {
+    if (ex.sinks) {
+        const float s2 = ex.sinks[h] * 1.4426950408889634f;
+        if (s2 <= m) {
+            den += exp2f(s2 - m);
+        } else {
+            const float w = exp2f(m - s2);
+            den = den * w + 1.0f;
+            num *= w;
+        }
+    }
+    float r = num / den;
+    if (ex.gate) r *= 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.gate_stride + h]));
+    return r;
+}
+
+template <int D, bool FUSE, bool WIDE>
 __global__ void __launch_bounds__(RD_THREADS + 32)
 attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                              const bf16* __restrict__ q, int q_stride, const int* __restrict__ block_table,
                              int max_pages, const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                              float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out,
                              int n_splits, int nh, int nkv, int G, int page_size, int window, float scale_log2e,
-                             int* __restrict__ err, const RdRope rp) {
+                             int* __restrict__ err, const RdRope rp, const RdExtras ex) {
     constexpr int STAGES = 384 / D;
     constexpr int CH = D / 8, KS = D / 16, NT_D = D / 8;
     constexpr unsigned TILE_BYTES = RD_BN * D * 2;            // a K tile, or a V tile
@@ -359,7 +386,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 m_run[e] = m_new;
                 l_run[e] *= alpha[e];
             }
-            unsigned pf[4];
+            unsigned pf[4], pl[4];
 #pragma unroll
             for (int nt = 0; nt < 2; nt++) {
                 const float p0 = fast_exp2(sc[nt][0] - mref[0]), p1 = fast_exp2(sc[nt][1] - mref[0]);
@@ -368,6 +395,10 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 l_run[1] += p2 + p3;
                 pf[nt * 2] = rd_pack(p0, p1);
                 pf[nt * 2 + 1] = rd_pack(p2, p3);
+                if (WIDE) {     // what the rounding took away
+                    pl[nt * 2] = rd_pack(p0 - __uint_as_float(pf[nt * 2] << 16), p1 - __uint_as_float(pf[nt * 2] & 0xffff0000u));
+                    pl[nt * 2 + 1] = rd_pack(p2 - __uint_as_float(pf[nt * 2 + 1] << 16), p3 - __uint_as_float(pf[nt * 2 + 1] & 0xffff0000u));
+                }
             }
             if (key0 + 15 > p || key0 < lo) {
                 // a tile at the edge of the range: V rows of hidden keys may hold anything (another
@@ -396,6 +427,10 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
                 o[np * 2 + 1][3] *= alpha[1];
                 rd_mma(o[np * 2], pf, b0, b1);
                 rd_mma(o[np * 2 + 1], pf, b2, b3);
+                if (WIDE) {
+                    rd_mma(o[np * 2], pl, b0, b1);
+                    rd_mma(o[np * 2 + 1], pl, b2, b3);
+                }
             }
         }
         __syncwarp();
@@ -441,7 +476,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
         }
         const size_t head = (size_t)t * nh + hk * G + r;
         if (n_splits == 1) {
-            out[head * D + c] = __float2bfloat16_rn(num / den);
+            out[head * D + c] = __float2bfloat16_rn(rd_finish(num, den, M, ex, t, hk * G + r));
         } else {
             const size_t oidx = head * n_splits + split;
             part_acc[oidx * D + c] = num;
@@ -458,7 +493,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __
 template <int D>
 __global__ void attention_decode_ring_merge_kernel(const float* __restrict__ part_acc,
                                                    const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                                   int n_splits, int nh) {
+                                                   int n_splits, int nh, const RdExtras ex) {
     pdl_grid_sync();
     const int h = blockIdx.x, t = blockIdx.y, c = threadIdx.x;
     const size_t o = ((size_t)t * nh + h) * n_splits;
@@ -472,7 +507,7 @@ __global__ void attention_decode_ring_merge_kernel(const float* __restrict__ par
         den += part_ml[(o + s) * 2 + 1] * w;
         num += part_acc[(o + s) * D + c] * w;
     }
-    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(num / den);
+    out[((size_t)t * nh + h) * D + c] = __float2bfloat16_rn(rd_finish(num, den, M, ex, t, h));
 }
 
 // ---- host side
@@ -511,7 +546,7 @@ template <int D>
 static int rd_launch(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages,
                      const int* block_table, int max_pages, const int* token_pos, const int* token_seq,
                      float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int page_size, int window,
-                     float scale, int n_splits, int* err, cudaStream_t s, const RdRope* rope) {
+                     float scale, int n_splits, int* err, cudaStream_t s, const RdRope* rope, const RdExtras* extras, bool wide) {
     CUtensorMap mk, mv;
     int rc;
     const long long rows = n_pages * nkv * page_size;
@@ -521,25 +556,29 @@ static int rd_launch(const void* q, int q_stride, const void* kc, const void* vc
     const size_t smem = (size_t)STAGES * 2 * RD_BN * D * 2 + (size_t)16 * D * 2 + 1024;
     RdRope rp = {};
     if (rope) rp = *rope;
+    RdExtras ex = {};
+    if (extras) ex = *extras;
+    if (rope && (wide || extras)) return ILLM_ERR_BAD_ARG;      // the fused form is the plain attention's
     auto launch = [&](auto kern) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         illm_launch(kern, dim3(n_splits, nkv, T), dim3(rope ? RD_THREADS + 32 : RD_THREADS), smem, s, mk, mv, (const bf16*)q, q_stride,
                     block_table, max_pages, token_pos, token_seq, part_acc, part_ml, (bf16*)out, n_splits, nh, nkv,
-                    nh / nkv, page_size, window, scale * 1.4426950408889634f, err, rp);
+                    nh / nkv, page_size, window, scale * 1.4426950408889634f, err, rp, ex);
         return illm_launch_status();
     };
-    rc = rope ? launch(attention_decode_ring_kernel<D, true>) : launch(attention_decode_ring_kernel<D, false>);
+    rc = rope ? launch(attention_decode_ring_kernel<D, true, false>)
+              : wide ? launch(attention_decode_ring_kernel<D, false, true>) : launch(attention_decode_ring_kernel<D, false, false>);
     if (rc != 0 || n_splits == 1) return rc;
     illm_launch(attention_decode_ring_merge_kernel<D>, dim3(nh, T), dim3(D), 0, s, (const float*)part_acc,
-                (const float*)part_ml, (bf16*)out, n_splits, nh);
+                (const float*)part_ml, (bf16*)out, n_splits, nh, ex);
     return illm_launch_status();
 }
 
 static int rd_run(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages,
                   const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc,
                   float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale,
-                  int n_splits, int* err, void* stream, const RdRope* rope) {
+                  int n_splits, int* err, void* stream, const RdRope* rope, const RdExtras* extras = nullptr, bool wide = false) {
     if (T <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || T > 65535 || nkv > 65535 || (q_stride & 7) || page_size % RD_BN ||
         n_splits < 1 || n_splits > RD_MAX_SPLITS || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
@@ -549,10 +588,10 @@ static int rd_run(const void* q, int q_stride, const void* kc, const void* vc, l
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 128)
         return rd_launch<128>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
-                              part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope);
+                              part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope, extras, wide);
     if (d == 64)
         return rd_launch<64>(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc,
-                             part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope);
+                             part_ml, out, T, nh, nkv, page_size, window, scale, n_splits, err, s, rope, extras, wide);
     return ILLM_ERR_BAD_ARG;
 }
 
@@ -566,6 +605,18 @@ extern "C" int illm_attention_decode_ring(const void* q, int q_stride, const voi
                                           int window, float scale, int n_splits, int* err, void* stream) {
     return rd_run(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc, part_ml, out, T,
                   nh, nkv, d, page_size, window, scale, n_splits, err, stream, nullptr);
+}
+
+// The same with sinks, gates (either may be nullptr) and, with wide_p, two-term softmax weights.
+extern "C" int illm_attention_decode_ring_ex(const void* q, int q_stride, const void* kc, const void* vc,
+                                             long long n_pages, const int* block_table, int max_pages,
+                                             const int* token_pos, const int* token_seq, float* part_acc,
+                                             float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size,
+                                             int window, float scale, int n_splits, int* err, int wide_p, const float* sinks,
+                                             const float* gate, int gate_stride, void* stream) {
+    RdExtras ex{sinks, gate, gate_stride};
+    return rd_run(q, q_stride, kc, vc, n_pages, block_table, max_pages, token_pos, token_seq, part_acc, part_ml, out, T,
+                  nh, nkv, d, page_size, window, scale, n_splits, err, stream, nullptr, &ex, wide_p != 0);
 }
 
 // The same with the position encoding and the cache write inside: `qkv` is the unrotated packed

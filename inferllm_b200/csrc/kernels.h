@@ -20,6 +20,7 @@ int illm_attention_decode_gqa(const void* q, int q_stride, const void* kc, const
 
 // attention_decode_ring.cu
 int illm_attention_decode_ring(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_splits, int* err, void* stream);
+int illm_attention_decode_ring_ex(const void* q, int q_stride, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_splits, int* err, int wide_p, const float* sinks, const float* gate, int gate_stride, void* stream);
 int illm_attention_decode_ring_rope(const void* qkv, const float* partials, int splits, long long split_stride, const float* cos_sin, int rot, int table_positions, int write_kv, void* kc, void* vc, long long n_pages, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, float* part_acc, float* part_ml, void* out, int T, int nh, int nkv, int d, int page_size, int window, float scale, int n_splits, int* err, int* step_err, void* stream);
 
 // attention_generic.cu

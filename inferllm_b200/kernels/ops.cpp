@@ -488,7 +488,8 @@ Mat attention_decode_gqa(Device& dev, const Mat& qkv, const KVView& kv, const St
 }
 
 Mat attention_decode_ring(Device& dev, const MatOrPartials& in, const KVView& kv, const StepView& ctx, Geometry g, float scale,
-                          long long max_len, int splits, const FusedRope* rope) {
+                          long long max_len, int splits, const FusedRope* rope, const AttentionExtras* extras) {
+    if (rope && extras) throw KernelError("attention_decode_ring: sinks and gates do not go with the fused position encoding");
     long long T, width;
     if (in.is_partials()) {
         if (!rope) throw KernelError("attention_decode_ring: unreduced slices need the fused position encoding");
@@ -510,6 +511,16 @@ Mat attention_decode_ring(Device& dev, const MatOrPartials& in, const KVView& kv
         if (n > 1) {
             part_acc = dev.alloc_n<float>((size_t)(t1 - t0) * g.n_heads * n * g.head_dim);
             part_ml = dev.alloc_n<float>((size_t)(t1 - t0) * g.n_heads * n * 2);
+        }
+        if (extras) {
+            check_kernel(illm_attention_decode_ring_ex(row_ptr(in.m, t0), (int)width, kv.k, kv.v, kv.num_pages, kv.block_table, kv.width,
+                                                       ctx.token_pos + t0, ctx.token_seq + t0, part_acc, part_ml, row_ptr(out, t0), (int)(t1 - t0),
+                                                       g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size, kv.window, scale, n, dev.tc_error_word(),
+                                                       extras->wide_weights ? 1 : 0, extras->sinks,
+                                                       extras->gate ? extras->gate + (size_t)t0 * extras->gate_stride : nullptr, extras->gate_stride,
+                                                       dev.stream()),
+                         "attention_decode_ring");
+            continue;
         }
         if (!rope) {
             check_kernel(illm_attention_decode_ring(row_ptr(in.m, t0), (int)width, kv.k, kv.v, kv.num_pages, kv.block_table, kv.width,
@@ -575,6 +586,11 @@ Mat attention_decode_ex(Device& dev, const Mat& qkv, const KVView& kv, const Ste
 Mat attention_ex(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, Geometry g, float scale, const AttentionExtras& ex) {
     const int dv = kv.v_head_dim > 0 ? kv.v_head_dim : g.head_dim;
     if (q.dtype == DType::BF16 && dv == g.head_dim) {
+        if (ctx.is_decode && attention_decode_ring_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size)) {
+            MatOrPartials in;
+            in.m = q;
+            return attention_decode_ring(dev, in, kv, ctx, g, scale, ctx.max_seq_len, 0, nullptr, &ex);
+        }
         if (ctx.is_decode && attention_decode_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size))
             return attention_decode_ex(dev, q, kv, ctx, g, scale, ctx.max_seq_len, ex);
         if (!ctx.is_decode && attention_prefill_tc_supported(q.dtype, g.n_heads, g.n_kv_heads, g.head_dim, kv.page_size))

@@ -158,7 +158,7 @@ Mat attention_decode(Device& dev, const Mat& qkv, const KVView& kv, const StepVi
 Mat attention_decode_gqa(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale, long long max_len);
 struct FusedRope { const float* cos_sin; int rot_dim; long long n_pos; bool write_kv; int* step_err; };
 Mat attention_decode_ring(Device& dev, const MatOrPartials& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
-                          long long max_len, int splits /* 0: by policy */, const FusedRope* rope);
+                          long long max_len, int splits /* 0: by policy */, const FusedRope* rope, const AttentionExtras* extras = nullptr);
 Mat attention_prefill(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale);
 Mat attention_prefill_tc(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx, Geometry g, float scale,
                          const AttentionExtras* extras = nullptr);
