@@ -192,7 +192,15 @@ class LlamaConfig(LibraryConfig):
         return super().__getattr__(name)
 
 
-_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig}
+class VokelixConfig(LibraryConfig):
+    """The Vokelix decoder (`config/vokelix.h`): `layers` (a list of {type: "attention" | "lightning" |
+    "retention", mixer: {...}, mlp: {kind: "dense", ff} or None}), `width`, `vocab`, `norm` ({eps}),
+    `postln_alpha`, and optionally `max_positions`.  The dictionary names the class under `architecture`."""
+
+    architecture = "Vokelix"
+
+
+_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig}
 _CALLBACKS = {}      # name -> (ctypes callback, holder of the last returned text): kept alive while registered
 
 
@@ -235,7 +243,7 @@ def register_architecture(name: str, config_cls: type, aliases=()):
 def unregister_architecture(name: str):
     _b.check(_b.lib().illm_unregister_architecture(name.encode()))
     _CALLBACKS.pop(name, None)
-    if _PY_CLASSES.get(name) is not LlamaConfig:
+    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig):
         _PY_CLASSES.pop(name, None)
 
 

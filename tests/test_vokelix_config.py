@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import plain_vokelix as pv
 
-from inferllm_b200 import ConfigError, config_from_dict
+from inferllm_b200 import ConfigError, VokelixConfig, config_from_dict
 from inferllm_b200.weights import tensor_decls
 
 
@@ -43,6 +43,14 @@ def test_spec_carries_every_size_and_constant():
         assert (n["eps"], n["weight_offset"], n["residual_scale"]) == (2e-5, 1.0, 3.5)
     assert spec.layers[0].ffn["intermediate_size"] == 72 and spec.layers[2].ffn.kind == ""
     assert spec.final_norm["weight_offset"] == 1.0
+
+
+def test_the_python_face_is_typed_and_round_trips():
+    cfg = cfg_of(layer_types=("lightning", "attention"), width=40)
+    c = config_from_dict(cfg)
+    assert isinstance(c, VokelixConfig) and c.architecture == "Vokelix"
+    assert (c.width, c.vocab, c.postln_alpha) == (40, cfg["vocab"], cfg["postln_alpha"]) and len(c.layers) == 2
+    assert VokelixConfig.from_dict(c.to_dict()) == c
 
 
 def test_declared_tensors_are_the_files_names_and_shapes():

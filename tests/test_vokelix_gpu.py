@@ -9,6 +9,7 @@ one (a token far back still counts) and far from one.
 import json
 import os
 import struct
+import subprocess
 
 import numpy as np
 import pytest
@@ -342,3 +343,21 @@ def test_greedy_generation_through_the_model_api(name, models):
     m16.init(top_k=0, top_p=1.0, temp=0.0, repeat_penalty=1.0, repeat_last_n=0, seed=0, end_token=-1)
     got16 = m16.generate(prompts, max_new_tokens=12, stop_ids=[]).tokens
     assert [g[0] for g in got16] == [x[0] for x in want]        # later tokens may turn at a near-tie in bfloat16
+
+
+def test_command_line(models):
+    """bin/llama on a Vokelix folder: greedy tokens of two requests, float32."""
+    d, cfg, w = models["other"]
+    prompts = [prompt(cfg, n, 80 + n) for n in (4, 21)]
+    want = [pv.greedy_generate(cfg, w, p, 6) for p in prompts]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = [os.path.join(root, "bin", "llama"), "-m", d, "-d", "float32", "-c", "128", "-n", "6", "--temp", "0", "--top_k", "0",
+            "--top_p", "1", "--repeat_penalty", "1", "-s", "1"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(args, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    got = [[int(t) for t in ln.split(": ")[1].split(",")] for ln in r.stdout.splitlines() if ln.startswith("[")]
+    assert got == want
+    r = subprocess.run(args[:3] + ["--random-prompts", "5,9", "-n", "3", "-c", "64"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr        # the vocabulary size comes from the model's spec, whatever its key is called
