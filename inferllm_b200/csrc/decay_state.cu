@@ -59,6 +59,8 @@ struct DecayScanArgs {
     int tile;                       // tokens staged at a time
     int vec;                        // 16-byte copies are possible
     int inline_prep;                // the scan prepares q, k, v itself while it stages them (steps of few tokens)
+    int segments;                   // a sequence's tokens of this step in up to so many segments side by side (1: in order)
+    float* seg_state;               // [B, segments, nh, dv, d]: what each segment's own tokens add to the state
 };
 
 __device__ __forceinline__ float act_of(float v, int act) {
@@ -111,7 +113,16 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 }
 
 // R rows x C columns of the state per thread, the rows of a column group over LI lanes.
-template <int R, int C, int LI>
+//
+// Segments: a long prompt of few sequences leaves most of the GPU idle, because a sequence's tokens
+// are a chain.  With a.segments = P > 1 the chain is cut: pass 0 runs every segment of 16 k tokens on
+// its own, the first from the sequence's state, the others from zero, and leaves each segment's final
+// state in seg_state; pass 1 gives every later segment what it missed: the state at its start,
+// S_in = sum over earlier segments r of decay^(tokens between) S_r, enters its tokens' outputs as
+// o_t += decay^(t - t0 + 1) S_in^T q_t (no chain: the tokens are independent), and the last segment
+// writes the sequence's state.  The sums then have another order than token by token, so the float32
+// mode, which promises the same bits however a prompt is cut, never asks for segments.
+template <int R, int C, int LI, int PASS>
 __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float sm[];
@@ -120,8 +131,14 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     constexpr int JB = JW * (DS_THREADS / 32);      // columns per block
     constexpr int DP = R * LI;                      // rows with padding
     constexpr int ROW = 2 * DP + JB;                // floats of one staged token: q, k, v
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * JB;
+    const int P = a.segments;
+    const int b = blockIdx.x / P, seg = blockIdx.x % P, h = blockIdx.y, j0 = blockIdx.z * JB;
     const int d = a.d, dv = a.dv;
+    const int q0 = a.cu_q[b], q1 = a.cu_q[b + 1];
+    const int seg_len = P > 1 ? (((q1 - q0 + P - 1) / P + 15) & ~15) : q1 - q0;      // whole tiles
+    const int t0 = q0 + seg * seg_len, t1 = t0 + seg_len < q1 ? t0 + seg_len : q1;
+    if (t0 >= t1) return;                                                           // a short sequence fills fewer segments
+    const bool last_seg = t1 == q1;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane % LI;
     const int jl = (warp * (32 / LI) + lane / LI) * C;      // first of this thread's columns within the block
@@ -131,25 +148,78 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     // row of register (m, r): m * 4 LI + 4 g + r, so that the LI lanes of a column group read 16-byte
     // pieces of q, k and the state that lie side by side
     float s[C][M][4];
+    // one thread's elements of a state [dv][d] at `src`, times `mul`, plus `add` (what it holds already) if asked
+    auto load_state = [&](const float* src, float mul, bool accumulate) {
 #pragma unroll
-    for (int c = 0; c < C; c++) {
-        const int j = j0 + jl + c;
+        for (int c = 0; c < C; c++) {
+            const int j = j0 + jl + c;
 #pragma unroll
-        for (int m = 0; m < M; m++) {
-            const int i = m * 4 * LI + 4 * g;
-            if (a.vec && j < dv && i < d) {
-                const float4 v4 = *reinterpret_cast<const float4*>(Sg + (size_t)j * d + i);
-                s[c][m][0] = v4.x; s[c][m][1] = v4.y; s[c][m][2] = v4.z; s[c][m][3] = v4.w;
-            } else {
+            for (int m = 0; m < M; m++) {
+                const int i = m * 4 * LI + 4 * g;
+                float v[4];
+                if (a.vec && j < dv && i < d) {
+                    const float4 v4 = *reinterpret_cast<const float4*>(src + (size_t)j * d + i);
+                    v[0] = v4.x; v[1] = v4.y; v[2] = v4.z; v[3] = v4.w;
+                } else {
 #pragma unroll
-                for (int r = 0; r < 4; r++) s[c][m][r] = (j < dv && i + r < d) ? Sg[(size_t)j * d + i + r] : 0.f;
+                    for (int r = 0; r < 4; r++) v[r] = (j < dv && i + r < d) ? src[(size_t)j * d + i + r] : 0.f;
+                }
+#pragma unroll
+                for (int r = 0; r < 4; r++) s[c][m][r] = accumulate ? fmaf(s[c][m][r], mul, v[r]) : v[r];
             }
         }
+    };
+    auto store_state = [&](float* dst) {
+#pragma unroll
+        for (int c = 0; c < C; c++) {
+            const int j = j0 + jl + c;
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const int i = m * 4 * LI + 4 * g;
+                if (a.vec && j < dv && i < d) {
+                    *reinterpret_cast<float4*>(dst + (size_t)j * d + i) = make_float4(s[c][m][0], s[c][m][1], s[c][m][2], s[c][m][3]);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+                        if (j < dv && i + r < d) dst[(size_t)j * d + i + r] = s[c][m][r];
+                }
+            }
+        }
+    };
+    auto power = [&](int n) {       // decay^n by n multiplications (n is a segment's length at most)
+        float f = 1.f;
+        for (int i = 0; i < n; i++) f *= dec;
+        return f;
+    };
+    float* seg_base = a.seg_state + ((size_t)b * P * a.nh + h) * (size_t)d * dv;      // + seg * nh * d * dv per segment
+    const size_t seg_stride = (size_t)a.nh * d * dv;
+    float factor = dec;             // pass 1: decay^(t - t0 + 1) of the token at hand
+    if (PASS == 0) {
+        if (seg == 0) {
+            load_state(Sg, 0.f, false);
+        } else {
+#pragma unroll
+            for (int c = 0; c < C; c++)
+#pragma unroll
+                for (int m = 0; m < M; m++)
+#pragma unroll
+                    for (int r = 0; r < 4; r++) s[c][m][r] = 0.f;
+        }
+    } else {
+        if (seg == 0) {             // nothing to correct; a sequence of one segment still has to get its state
+            if (last_seg) {
+                load_state(seg_base, 0.f, false);
+                store_state(Sg);
+            }
+            return;
+        }
+        const float dec_len = power(seg_len);
+        load_state(seg_base, 0.f, false);
+        for (int r = 1; r < seg; r++) load_state(seg_base + r * seg_stride, dec_len, true);
     }
     // rows beyond d and columns beyond dv stay zero in both buffers
     for (int idx = threadIdx.x; idx < 2 * a.tile * ROW; idx += DS_THREADS) sm[idx] = 0.f;
     __syncthreads();
-    const int t0 = a.cu_q[b], t1 = a.cu_q[b + 1];
     auto stage = [&](int buf, int tb) {
         const int n = t1 - tb < a.tile ? t1 - tb : a.tile;
         float* base = sm + buf * a.tile * ROW;
@@ -223,10 +293,12 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
                 const float4 kk = k4[m * LI], qq = q4[m * LI];
 #pragma unroll
                 for (int c = 0; c < C; c++) {
-                    s[c][m][0] = fmaf(dec, s[c][m][0], kk.x * v[c]);
-                    s[c][m][1] = fmaf(dec, s[c][m][1], kk.y * v[c]);
-                    s[c][m][2] = fmaf(dec, s[c][m][2], kk.z * v[c]);
-                    s[c][m][3] = fmaf(dec, s[c][m][3], kk.w * v[c]);
+                    if (PASS == 0) {
+                        s[c][m][0] = fmaf(dec, s[c][m][0], kk.x * v[c]);
+                        s[c][m][1] = fmaf(dec, s[c][m][1], kk.y * v[c]);
+                        s[c][m][2] = fmaf(dec, s[c][m][2], kk.z * v[c]);
+                        s[c][m][3] = fmaf(dec, s[c][m][3], kk.w * v[c]);
+                    }
                     p[u][c] = fmaf(s[c][m][0], qq.x, p[u][c]);
                     p[u][c] = fmaf(s[c][m][1], qq.y, p[u][c]);
                     p[u][c] = fmaf(s[c][m][2], qq.z, p[u][c]);
@@ -263,14 +335,18 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
             }
         }
         // lanes that differ only in the bits of the plain steps hold the same sum: one of them writes
-        if ((lane & plain_bits) == 0) {
 #pragma unroll
-            for (int u = 0; u < U; u++) {
+        for (int u = 0; u < U; u++) {
+            if ((lane & plain_bits) == 0) {
                 float* orow = a.out + (size_t)(t + u) * a.nh * dv + (size_t)h * dv + j0 + jl + first;
 #pragma unroll
                 for (int c = 0; c < C; c++)
-                    if (c < nc && j0 + jl + first + c < dv) orow[c] = p[u][c];
+                    if (c < nc && j0 + jl + first + c < dv) {
+                        if (PASS == 0) orow[c] = p[u][c];
+                        else orow[c] += factor * p[u][c];
+                    }
             }
+            if (PASS == 1) factor *= dec;
         }
     };
     if (t0 < t1) stage(0, t0);
@@ -293,20 +369,32 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
         for (; tt < n; tt++) tokens(std::integral_constant<int, 1>(), base + tt * ROW, tb + tt);
         __syncthreads();        // the buffer is filled again by the tile after the next
     }
+    if (PASS == 0) {
+        store_state(P > 1 ? seg_base + seg * seg_stride : Sg);
+    } else if (last_seg) {
+        // the sequence's state: what came in, decayed over this segment, plus what the segment added
+        const float dec_own = power(t1 - t0);
 #pragma unroll
-    for (int c = 0; c < C; c++) {
-        const int j = j0 + jl + c;
+        for (int c = 0; c < C; c++)
 #pragma unroll
-        for (int m = 0; m < M; m++) {
-            const int i = m * 4 * LI + 4 * g;
-            if (a.vec && j < dv && i < d) {
-                *reinterpret_cast<float4*>(Sg + (size_t)j * d + i) = make_float4(s[c][m][0], s[c][m][1], s[c][m][2], s[c][m][3]);
-            } else {
+            for (int m = 0; m < M; m++)
 #pragma unroll
-                for (int r = 0; r < 4; r++)
-                    if (j < dv && i + r < d) Sg[(size_t)j * d + i + r] = s[c][m][r];
-            }
-        }
+                for (int r = 0; r < 4; r++) s[c][m][r] *= dec_own;
+        float own[C][M][4];
+#pragma unroll
+        for (int c = 0; c < C; c++)
+#pragma unroll
+            for (int m = 0; m < M; m++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) own[c][m][r] = s[c][m][r];
+        load_state(seg_base + seg * seg_stride, 0.f, false);
+#pragma unroll
+        for (int c = 0; c < C; c++)
+#pragma unroll
+            for (int m = 0; m < M; m++)
+#pragma unroll
+                for (int r = 0; r < 4; r++) s[c][m][r] += own[c][m][r];
+        store_state(Sg);
     }
 }
 
@@ -322,18 +410,25 @@ static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
     int tile = (int)(40 * 1024 / sizeof(float) / (2 * ROW));
     a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
-    if (smem > 48 * 1024) cudaFuncSetAttribute(decay_scan_kernel<R, C, LI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    illm_launch(decay_scan_kernel<R, C, LI>, dim3(B, a.nh, (a.dv + JB - 1) / JB), dim3(DS_THREADS), smem, s, a);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decay_scan_kernel<R, C, LI, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    const dim3 grid(B * a.segments, a.nh, (a.dv + JB - 1) / JB);
+    illm_launch(decay_scan_kernel<R, C, LI, 0>, grid, dim3(DS_THREADS), smem, s, a);
+    if (a.segments > 1) illm_launch(decay_scan_kernel<R, C, LI, 1>, grid, dim3(DS_THREADS), smem, s, a);
 }
 
 // x: the packed projection; its q, k and v columns are prepared in place (T rows).
 extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act,
                                const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots,
-                               const int* cu_q, const int* token_pos, float* out, int B, int* err, void* stream) {
+                               const int* cu_q, const int* token_pos, float* out, int B, int* err, int segments, float* seg_state,
+                               void* stream) {
     if (B <= 0 || T <= 0) return 0;
+    if (segments < 1 || (segments > 1 && !seg_state) || (long long)B * segments > 0x7fffffff) return ILLM_ERR_BAD_ARG;
     if (nh <= 0 || d <= 0 || d > 1024 || dv <= 0 || nh > 65535 || rot < 0 || rot > d || (rot & 1) || (rot && !cos_sin) || !x || !state || !out)
         return ILLM_ERR_BAD_ARG;
-    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0};
+    DecayScanArgs a{x, ld, q_off, k_off, v_off, nh, d, dv, qk_act, v_act, cos_sin, rot, n_pos, k_scale, decay, state, slots, cu_q, token_pos, out, err, 0, 0, 0, segments, seg_state};
     a.vec = !((d | dv | ld | q_off | k_off | v_off) & 3) && !((uintptr_t)x & 15) && !((uintptr_t)state & 15);
     cudaStream_t s = (cudaStream_t)stream;
     // a step of few tokens (single tokens of a batch) is not worth a launch of its own for the preparation

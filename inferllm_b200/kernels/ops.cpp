@@ -433,6 +433,13 @@ Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepVi
 
 bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }      // head sizes up to 1024
 
+int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms) {
+    const long long blocks = (long long)B * n_heads * ceil_div(v_head_dim, 16);
+    long long P = std::min<long long>(8, (2LL * n_sms) / std::max<long long>(blocks, 1));
+    P = std::min<long long>(P, max_q / 128);
+    return P < 2 ? 1 : (int)P;
+}
+
 Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ctx, const StateView& st) {
     need(x, "the packed projection", true, DType::F32);
     if (!st.state || st.dtype != DType::F32 || st.elements != (long long)p.n_heads * p.head_dim * p.v_head_dim)
@@ -441,9 +448,11 @@ Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ct
         throw KernelError("decay_scan: a state of " + std::to_string(p.head_dim) + " x " + std::to_string(p.v_head_dim) +
                           " per head is beyond the kernel (head sizes up to 1024)");
     Mat out = new_mat_exact(dev, x.rows, (long long)p.n_heads * p.v_head_dim, DType::F32);
+    const int segments = (p.in_order || ctx.is_decode) ? 1 : decay_scan_segments(ctx.B, p.n_heads, p.v_head_dim, ctx.max_q, dev.n_sms());
+    float* seg_state = segments > 1 ? dev.alloc_n<float>((size_t)ctx.B * segments * p.n_heads * p.head_dim * p.v_head_dim) : nullptr;
     check_kernel(illm_decay_scan((float*)x.p, (int)x.rows, (int)x.cols, p.q_off, p.k_off, p.v_off, p.n_heads, p.head_dim, p.v_head_dim, p.qk_act, p.v_act,
                                  p.rot_dim ? p.cos_sin : nullptr, p.rot_dim, (int)p.n_pos, p.k_scale, p.decay, (float*)st.state, st.slots, ctx.cu_q,
-                                 ctx.token_pos, (float*)out.p, ctx.B, ctx.err, dev.stream()),
+                                 ctx.token_pos, (float*)out.p, ctx.B, ctx.err, segments, seg_state, dev.stream()),
                  "decay_scan");
     return out;
 }

@@ -206,7 +206,13 @@ struct DecayScan {
     long long n_pos = 0;
     float k_scale = 1.f;
     const float* decay = nullptr;       // float32 [heads] on the device
+    // false: a long prompt of few sequences may be cut into segments that run side by side (the order of
+    // the sums then differs from token by token); true: always in order, bit for bit
+    bool in_order = true;
 };
+// In how many segments a prompt step's sequences are cut: enough to fill the GPU about twice, at most 8,
+// none shorter than 128 tokens; 1 for single tokens.
+int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms);
 Mat decay_scan(Device& dev, const Mat& x_f32, const DecayScan& p, const StepView& ctx, const StateView& st);
 bool decay_scan_supported(int head_dim, int v_head_dim);
 // y = o / sqrt(mean over groups of `group` columns (o^2) + eps) (* w) * act(gate), gate_act 1: silu, 2: sigmoid

@@ -116,6 +116,7 @@ struct DecayLinearAttention : Mixer {
         p.v_act = v_act;
         p.k_scale = k_scale;
         p.decay = (const float*)decay_buf.get();
+        p.in_order = rt->is_f32();      // the float32 mode gives the same bits however a prompt is cut
         const float* table = nullptr;
         int rot = 0;
         long long n_pos = 0;

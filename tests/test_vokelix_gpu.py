@@ -325,6 +325,34 @@ def test_state_far_back_survives(tmp_path):
             assert_close(in_portions(eng, ids, [500, 2, 1]), ref, dtype, f"{kind} portions")
 
 
+def test_long_prompts_in_segments(tmp_path):
+    """In the bfloat16 mode a long prompt's recurrence is cut into segments that run side by side and are
+    joined afterwards (the float32 mode keeps the order, bit for bit).  Prompts whose lengths leave the
+    last segment short, fill only some segments, or are a single token, together in one step; then each
+    goes on token by token from the state the joined segments left."""
+    rng = np.random.default_rng(4)
+    cfg = with_max_positions(pv.random_config(rng, ("retention", "lightning"), lin_heads=2, decay=[0.98, 0.75], lin_dim=16, lin_vdim=24,
+                                              ret_rot_dims=8), 2048)
+    d = str(tmp_path)
+    w = write_model(d, cfg, 23)
+    lens = [1500, 1, 257, 1024, 130]
+    reqs = [prompt(cfg, n + 5, 70 + i) for i, n in enumerate(lens)]
+    refs = [pv.forward(cfg, w, ids) for ids in reqs]
+    for dtype in DTYPES:
+        eng = engine(d, dtype, max_tokens=4096, max_seq_len=2048)
+        slots = [eng.new_sequence() for _ in reqs]
+        lg = eng.step([StepItem(s, ids[:n], list(range(n))) for s, ids, n in zip(slots, reqs, lens)]).cpu().numpy()
+        off = 0
+        for ids, n, ref in zip(reqs, lens, refs):
+            assert_close(lg[off:off + n], ref[:n], dtype, f"prompt of {n} tokens among others")
+            off += n
+        for k in range(5):
+            lg = eng.step([StepItem(s, [ids[n + k]], [0]) for s, ids, n in zip(slots, reqs, lens)]).cpu().numpy()
+            for i, (n, ref) in enumerate(zip(lens, refs)):
+                assert_close(lg[i:i + 1], ref[n + k:n + k + 1], dtype, f"token {k} behind a prompt of {n}")
+        eng.check_device_errors()
+
+
 # ------------------------------------------------------------------ the library's own entry point
 
 
