@@ -15,15 +15,15 @@
 //
 // decay_scan_kernel: the columns of S evolve independently of one another (S[:, j] only ever meets
 // v[j]), so a block owns one (sequence, head, group of columns) and a thread keeps its part of the
-// state in registers for the whole step: R rows of C columns (R C = 32; four rows of eight columns up
-// to head size 128, so that a token costs a thread few shared-memory reads per FMA), the rows of a
-// column group dealt to LI neighbouring lanes (R LI >= d, rows beyond d are zeros).  The step's
+// state in registers for the whole step: R rows of C columns (16 rows of four columns up to head
+// size 512, so that a token costs a thread few shared-memory reads per FMA), the rows of a column
+// group dealt to LI neighbouring lanes (R LI >= d, rows beyond d are zeros).  The step's
 // tokens come in tiles through two shared-memory buffers filled by cp.async, the next tile on its
 // way while this one is used; every thread runs a tile's tokens one after the other without any
-// synchronisation: 32 independent chains s = decay s + k v[j], its parts of o_t[j] = sum_i s q[i], and
+// synchronisation: 64 independent chains s = decay s + k v[j], its parts of o_t[j] = sum_i s q[i], and
 // a fixed tree of shuffles over the LI lanes of the column group.  What bounds it is the float32 FMA rate
-// and the latency of the chain, not memory; a prompt of one sequence fills heads x dv / (128 / LI)
-// blocks.  The state is stored column by column ([slots, heads, dv, d]), so that a thread's rows are
+// and the latency of the chain, not memory; a prompt of one sequence fills heads x dv / (512 / LI)
+// blocks (times its segments, see below).  The state is stored column by column ([slots, heads, dv, d]), so that a thread's rows are
 // 16-byte pieces.
 //
 // The recurrence is float32 throughout, in the float32 mode and in the bfloat16 mode alike, because
@@ -38,9 +38,6 @@
 
 #define DS_THREADS 128
 #define DS_MAX_TILE 16
-#ifndef DS_C128
-#define DS_C128 4          // columns per thread at head sizes 65..128
-#endif
 #define DS_U 4             // tokens whose reductions are interleaved
 
 struct DecayScanArgs {
@@ -373,27 +370,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
         store_state(P > 1 ? seg_base + seg * seg_stride : Sg);
     } else if (last_seg) {
         // the sequence's state: what came in, decayed over this segment, plus what the segment added
-        const float dec_own = power(t1 - t0);
-#pragma unroll
-        for (int c = 0; c < C; c++)
-#pragma unroll
-            for (int m = 0; m < M; m++)
-#pragma unroll
-                for (int r = 0; r < 4; r++) s[c][m][r] *= dec_own;
-        float own[C][M][4];
-#pragma unroll
-        for (int c = 0; c < C; c++)
-#pragma unroll
-            for (int m = 0; m < M; m++)
-#pragma unroll
-                for (int r = 0; r < 4; r++) own[c][m][r] = s[c][m][r];
-        load_state(seg_base + seg * seg_stride, 0.f, false);
-#pragma unroll
-        for (int c = 0; c < C; c++)
-#pragma unroll
-            for (int m = 0; m < M; m++)
-#pragma unroll
-                for (int r = 0; r < 4; r++) s[c][m][r] += own[c][m][r];
+        load_state(seg_base + seg * seg_stride, power(t1 - t0), true);
         store_state(Sg);
     }
 }
@@ -407,7 +384,7 @@ extern "C" long long illm_decay_scan_smem(int d, int dv) {
 template <int R, int C, int LI>
 static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {
     constexpr int DP = R * LI, JB = C * (32 / LI) * (DS_THREADS / 32), ROW = 2 * DP + JB;
-    int tile = (int)(40 * 1024 / sizeof(float) / (2 * ROW));
+    int tile = (int)(48 * 1024 / sizeof(float) / (2 * ROW));
     a.tile = tile > DS_MAX_TILE ? DS_MAX_TILE : (tile < 1 ? 1 : tile);
     const size_t smem = (size_t)2 * a.tile * ROW * sizeof(float);
     if (smem > 48 * 1024) {
@@ -434,16 +411,17 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     // a step of few tokens (single tokens of a batch) is not worth a launch of its own for the preparation
     a.inline_prep = T <= 64 ? 1 : 0;
     if (!a.inline_prep && (qk_act || v_act || rot || k_scale != 1.0f)) illm_launch(decay_prep_kernel, dim3(T, nh), dim3(128), 0, s, a);
-    // four rows x eight columns per thread up to head size 128 (fewest shared-memory reads per FMA); more rows beyond
-    if (d <= 4) decay_launch<4, 8, 1>(a, B, s);
-    else if (d <= 8) decay_launch<4, 8, 2>(a, B, s);
-    else if (d <= 16) decay_launch<4, 8, 4>(a, B, s);
-    else if (d <= 32) decay_launch<4, 8, 8>(a, B, s);
-    else if (d <= 64) decay_launch<4, 8, 16>(a, B, s);
-    else if (d <= 128) decay_launch<4, DS_C128, 32>(a, B, s);
-    else if (d <= 256) decay_launch<8, 4, 32>(a, B, s);
-    else if (d <= 512) decay_launch<16, 2, 32>(a, B, s);
-    else decay_launch<32, 1, 32>(a, B, s);
+    // 16 rows x 4 columns per thread (64 state elements in registers), the rows of a column group over d / 16 lanes:
+    // a token costs a thread four 16-byte reads of q and of k, few enough to be on their way a token ahead,
+    // and the lanes few shuffles.  (Measured against 4 x 4 over 32 lanes, 16 x 8 over 8 and 64 x 2 over 2 at
+    // head size 128.)
+    if (d <= 16) decay_launch<16, 4, 1>(a, B, s);
+    else if (d <= 32) decay_launch<16, 4, 2>(a, B, s);
+    else if (d <= 64) decay_launch<16, 4, 4>(a, B, s);
+    else if (d <= 128) decay_launch<16, 4, 8>(a, B, s);
+    else if (d <= 256) decay_launch<16, 4, 16>(a, B, s);
+    else if (d <= 512) decay_launch<16, 4, 32>(a, B, s);
+    else decay_launch<32, 2, 32>(a, B, s);
     return illm_launch_status();
 }
 

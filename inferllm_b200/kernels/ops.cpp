@@ -434,8 +434,8 @@ Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepVi
 bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }      // head sizes up to 1024
 
 int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms) {
-    const long long blocks = (long long)B * n_heads * ceil_div(v_head_dim, 16);
-    long long P = std::min<long long>(8, (2LL * n_sms) / std::max<long long>(blocks, 1));
+    const long long blocks = (long long)B * n_heads * ceil_div(v_head_dim, 64);      // a block covers 64 columns of a head
+    long long P = std::min<long long>(8, (4LL * n_sms) / std::max<long long>(blocks, 1));
     P = std::min<long long>(P, max_q / 128);
     return P < 2 ? 1 : (int)P;
 }
