@@ -105,6 +105,10 @@ CONFIGS = {
     "wide": lambda rng: pv.random_config(rng, ("attention", "lightning", "retention"), width=64, vocab=128, heads=4, kv_heads=1, dim=64,
                                          vdim=64, rot_dims=32, scale=0.6, lin_heads=2, lin_dim=32, lin_vdim=64, decay=[0.6, 0.999],
                                          ret_rot_dims=32, ff=96),
+    # the other head size of the tensor-core kernels, two query heads per kv head, linear heads of 128 x 128
+    "wide128": lambda rng: pv.random_config(rng, ("retention", "attention", "lightning", "attention"), share_from={3: 1}, width=96, vocab=150,
+                                            heads=4, kv_heads=2, dim=128, vdim=128, rot_dims=64, scale=0.5, lin_heads=2, lin_dim=128,
+                                            lin_vdim=128, decay=[0.9, 0.995], ret_rot_dims=64, ff=160),
 }
 
 
@@ -195,7 +199,7 @@ def test_long_decoding(dtype, models):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "other", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "other", "wide", "wide128"])
 def test_batches_of_unequal_requests_and_reuse(name, dtype, models):
     """Prompts of unequal lengths in one step, decoded together until each runs out; two batches one
     after the other on a cache that only holds one of them, freed pages poisoned: slots, pages and
