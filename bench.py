@@ -155,7 +155,7 @@ DESIGN_LAYERS = ("lightning", "attention", "retention", "attention_shared", "lig
 
 def vokelix_config(z, vocab=32000, max_positions=4096):
     att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["d"], vdim=z["d"], scale=z["d"] ** -0.5,
-               rot=dict(base=250000.0, dims=z["d"] // 2, scaling=dict(factor=2.0, original=1024, fast=32.0, slow=1.0)))
+               rot=dict(base=500000.0, dims=z["d"] // 2, scaling=dict(factor=4.0, original=4096, fast=16.0, slow=2.0)))
     layers, first_att = [], None
     for i, t in enumerate(DESIGN_LAYERS):
         mlp = dict(kind="dense", ff=z["ff"])
@@ -170,9 +170,9 @@ def vokelix_config(z, vocab=32000, max_positions=4096):
             H = z["lin_heads"]
             m = dict(heads=H, dim=z["lin_d"], vdim=z["lin_d"], decay=[1.0 - 2.0 ** -(5 + 5 * h / max(H - 1, 1)) for h in range(H)])
             if t == "retention":
-                m["rot"] = dict(base=1000000.0, dims=z["lin_d"])
+                m["rot"] = dict(base=10000.0, dims=z["lin_d"])
             layers.append(dict(type=t, mixer=m, mlp=mlp))
-    return dict(architecture="Vokelix", layers=layers, norm=dict(eps=1e-6), postln_alpha=2.0, vocab=vocab, width=z["width"],
+    return dict(architecture="Vokelix", layers=layers, norm=dict(eps=1e-5), postln_alpha=1.5, vocab=vocab, width=z["width"],
                 max_positions=max_positions)
 
 

@@ -103,7 +103,7 @@ CONFIGS = {
                                           decay=[0.97], ret_rot_dims=16, alpha=1.0, ff=48, no_mlp=[1], eps=1e-6),
     # head sizes the tensor-core kernels of other models take, one kv head for all query heads
     "wide": lambda rng: pv.random_config(rng, ("attention", "lightning", "retention"), width=64, vocab=128, heads=4, kv_heads=1, dim=64,
-                                         vdim=64, rot_dims=32, scale=0.6, lin_heads=2, lin_dim=32, lin_vdim=64, decay=[0.6, 0.999],
+                                         vdim=64, rot_dims=16, scale=0.6, lin_heads=3, lin_dim=32, lin_vdim=64, decay=[0.6, 0.998, 0.9],
                                          ret_rot_dims=32, ff=96),
     # the other head size of the tensor-core kernels, two query heads per kv head, linear heads of 128 x 128
     "wide128": lambda rng: pv.random_config(rng, ("retention", "attention", "lightning", "attention"), share_from={3: 1}, width=96, vocab=150,
