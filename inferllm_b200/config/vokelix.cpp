@@ -126,7 +126,12 @@ ModelSpec VokelixConfig::model_spec() const {
                                                {"names", name_map({{"gate", "gate"}, {"up", "up"}, {"down", "down"}})}}));
             l.norms["norm2"] = norm;
         } else {
-            l.block = "postnorm_mixer";       // no feed-forward and no second norm
+            // no feed-forward: the layer ends after norm1; should a weight file hold a norm2 for it all the same, it is applied
+            // to the scaled stream alone (the norm is declared optional)
+            l.block = "postnorm_mixer";
+            PartSpec norm2 = norm;
+            norm2.params.set("optional", true);
+            l.norms["norm2"] = norm2;
         }
         s.layers.push_back(l);
         s.schedule.push_back(ScheduleEntry{(int)i, cache, writes});

@@ -48,10 +48,11 @@ std::vector<std::pair<std::string, Part*>> DecoderModel::owners() const {
     return out;
 }
 
-std::vector<std::pair<std::string, TensorDecl>> DecoderModel::tensor_decls() const {
+std::vector<std::pair<std::string, TensorDecl>> DecoderModel::tensor_decls(bool include_optional) const {
     std::vector<std::pair<std::string, TensorDecl>> decls;
     for (auto& o : owners())
-        for (auto& d : o.second->tensors()) decls.emplace_back(o.first + d.first, d.second);
+        for (auto& d : o.second->tensors())
+            if (include_optional || !d.second.optional) decls.emplace_back(o.first + d.first, d.second);
     return decls;
 }
 

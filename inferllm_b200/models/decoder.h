@@ -25,7 +25,8 @@ public:
     DecoderModel(const ModelSpec& spec, Runtime* runtime);
 
     // Every tensor the model reads from a weight file, by its name there, in a fixed order.
-    std::vector<std::pair<std::string, TensorDecl>> tensor_decls() const;
+    // (tensors declared optional only if asked: a weight file is checked with them, a random model has none)
+    std::vector<std::pair<std::string, TensorDecl>> tensor_decls(bool include_optional = false) const;
     // `open(prefix)` gives the source of the tensors below a prefix; each part takes its own and packs
     // them, one part at a time.
     void load_tensors(const std::function<std::unique_ptr<TensorSource>(const std::string& prefix)>& open);

@@ -178,15 +178,26 @@ struct RMSNorm : Norm {
     long long size;
     float eps, weight_offset, residual_scale;
     std::string tensor;
+    bool optional, absent = false;
     OwnedMat weight;
     RMSNorm(const PartSpec& s, Runtime* rt)
             : Norm(s, rt), size(s.get_int("size")), eps((float)s.get_double("eps")), weight_offset((float)s.get_double("weight_offset", 0.0)),
-              residual_scale((float)s.get_double("residual_scale", 1.0)), tensor(s.get_string("tensor", "weight")) {
+              residual_scale((float)s.get_double("residual_scale", 1.0)), tensor(s.get_string("tensor", "weight")),
+              optional(s.get_bool("optional", false)) {
         if (size <= 0 || !(eps > 0)) throw ConfigError("rmsnorm: size and eps must be positive");
     }
     bool keeps_f32() const { return weight_offset != 0.f || spec.get_bool("float32_weight", false); }
-    TensorDecls tensors() const override { return {{tensor, TensorDecl{{size}, weight_offset == 1.f ? "matrix" : "norm"}}}; }
+    TensorDecls tensors() const override {
+        TensorDecl d{{size}, weight_offset == 1.f ? "matrix" : "norm"};
+        d.optional = optional;
+        return {{tensor, d}};
+    }
+    bool present() const override { return !absent; }
     void load(TensorSource& src) override {
+        if (optional && !src.has(tensor)) {        // `optional`: the file may leave the weight out, and the norm with it
+            absent = true;
+            return;
+        }
         if (!keeps_f32()) {
             // a weight stored in 32-bit stays 32-bit; bfloat16 stays bfloat16 (the kernel takes both)
             weight = fetch_owned(rt, src, tensor, src.kept_dtype(tensor), "a norm weight");
@@ -603,7 +614,8 @@ struct PreNormBlock : Block {
 // "postnorm" is the norm-after-the-sum layer:
 //     x = norm1(a x + mixer(x));  x = norm2(a x + ffn(x))
 // The sublayers read the stream itself, and the normed sum replaces it; the factor a is the norms'
-// `residual_scale`.  "postnorm_mixer" is the same layer without a feed-forward (and without norm2).
+// `residual_scale`.  "postnorm_mixer" is the same layer without a feed-forward; its norm2 is given as an
+// optional norm and used only if the weight file has it: x = norm2(a x).
 struct PostNormBlock : Block {
     void forward(ResidualStream& stream, const StepContext& ctx, const CacheView& cache, bool writes) override {
         if (!stream.h.p) {      // the first layer: the embedding's rows in the compute dtype
@@ -613,7 +625,13 @@ struct PostNormBlock : Block {
         // the outputs only go into the norm's sum, so they may stay unreduced K slices
         stream.add(mixer->forward(stream.h, ctx, cache, writes, true));
         stream.h = norms.at("norm1")->forward_into_stream(stream);
-        if (!ffn) return;
+        if (!ffn) {
+            // no feed-forward: the layer ends here, unless the weight file holds a second norm all the same, which then
+            // norms the scaled stream alone
+            auto n2 = norms.find("norm2");
+            if (n2 != norms.end() && n2->second->present()) stream.h = n2->second->forward_into_stream(stream);
+            return;
+        }
         stream.add(ffn->forward(stream.h, ctx, true));
         stream.h = norms.at("norm2")->forward_into_stream(stream);
     }
@@ -622,7 +640,7 @@ struct PostNormBlock : Block {
 void register_builtin_parts() {
     register_decay_parts(reg<Mixer>());
     block_reg()["postnorm"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
-    block_reg()["postnorm_mixer"] = BlockKind{{"norm1"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
+    block_reg()["postnorm_mixer"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
     reg<Norm>()["rmsnorm"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<Norm>(new RMSNorm(s, rt)); };
     reg<PositionEncoding>()["rope_half"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new RopeTable(s, rt, false)); };
     reg<PositionEncoding>()["rope_pairs"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<PositionEncoding>(new RopeTable(s, rt, true)); };

@@ -47,6 +47,8 @@ struct Runtime {
 struct TensorDecl {
     std::vector<long long> shape;
     std::string init = "matrix";
+    // true: a weight file may leave the tensor out (the part then does without it); random models have none
+    bool optional = false;
     long long numel() const { long long n = 1; for (long long s : shape) n *= s; return n; }
 };
 using TensorDecls = std::vector<std::pair<std::string, TensorDecl>>;     // in the part's own order
@@ -83,6 +85,8 @@ public:
     // tables) into dst, whose rows are `dst_row_elems` elements apart (0: contiguous).
     virtual void fetch_into(const std::string& name, void* dst, DType want, long long dst_row_elems = 0) = 0;
     virtual std::vector<long long> shape(const std::string& name) = 0;
+    // whether the source has the tensor at all (asked for tensors that were declared optional)
+    virtual bool has(const std::string& name) { return true; }
 };
 
 // A matrix owned by a part: a fresh persistent buffer filled from the source.
@@ -152,6 +156,8 @@ public:
     // Norm after the sum: stream.x <- norm(residual_scale * stream.x + pending), the norm's own
     // residual_scale; the normed rows ARE the stream from then on, and they are also returned in the
     // compute dtype for the sublayer that reads them next.  Only norms that can do this override it.
+    // false for a norm whose optional weight was not in the file: the block leaves the norm out
+    virtual bool present() const { return true; }
     virtual Mat forward_into_stream(ResidualStream& stream) { throw EngineError("norm '" + spec.kind + "' cannot replace the stream by its output"); }
 };
 

@@ -25,7 +25,7 @@ void check_names_and_shapes(const std::vector<std::pair<std::string, TensorDecl>
     for (auto& d : decls) by_name[d.first] = &d.second;
     std::vector<std::string> missing, unexpected, wrong;
     for (auto& d : by_name)
-        if (!records.count(d.first)) missing.push_back(d.first);
+        if (!records.count(d.first) && !d.second->optional) missing.push_back(d.first);
     for (auto& r : records)
         if (!by_name.count(r.first) && !ends_with(r.first, "rotary_emb.inv_freq")) unexpected.push_back(r.first);
     for (auto& d : by_name) {
@@ -55,7 +55,7 @@ DType storage_dtype(DType stored, DType runtime_dtype, const std::string& init) 
 
 void check_model_folder(const DecoderModel& model, const std::string& folder) {
     ModelFiles files = open_model_files(folder);
-    check_names_and_shapes(model.tensor_decls(), files.records);
+    check_names_and_shapes(model.tensor_decls(true), files.records);
 }
 
 // ---- sources
@@ -138,6 +138,7 @@ public:
         return storage_dtype(rec(name).dtype, rt_->dtype, it == inits_->end() ? "matrix" : it->second);
     }
     std::vector<long long> shape(const std::string& name) override { return rec(name).shape; }
+    bool has(const std::string& name) override { return records_->count(prefix_ + name) != 0; }
     void fetch_into(const std::string& name, void* dst, DType want, long long dst_row_elems) override {
         const TensorRecord& r = rec(name);
         if (r.numel() == 0) return;
@@ -168,6 +169,7 @@ public:
         return rt_->is_f32() ? DType::F32 : DType::BF16;
     }
     std::vector<long long> shape(const std::string& name) override { return decl(name).shape; }
+    bool has(const std::string& name) override { return decls_->count(prefix_ + name) != 0; }      // optional tensors are not made
     void fetch_into(const std::string& name, void* dst, DType want, long long dst_row_elems) override {
         const TensorDecl& d = decl(name);
         if (d.numel() == 0) return;
@@ -198,7 +200,7 @@ private:
 void load_model_weights(DecoderModel& model, const std::string& folder) {
     if (!model.rt) throw EngineError("a model without a device cannot take weights");
     ModelFiles files = open_model_files(folder);
-    auto decls = model.tensor_decls();
+    auto decls = model.tensor_decls(true);
     check_names_and_shapes(decls, files.records);
     std::map<std::string, std::string> inits;
     for (auto& d : decls) inits[d.first] = d.second.init;

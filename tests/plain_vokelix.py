@@ -202,6 +202,8 @@ def forward(cfg, w, ids, return_layers=False):
         x = norm_one_plus(alpha * x + y, w[f"l{i}.norm1"], eps)
         if layer.get("mlp") is not None:
             x = norm_one_plus(alpha * x + gated_feed_forward(x, w, f"l{i}.mlp."), w[f"l{i}.norm2"], eps)
+        elif f"l{i}.norm2" in w:        # a file that holds a second norm for a layer without feed-forward
+            x = norm_one_plus(alpha * x, w[f"l{i}.norm2"], eps)
         after.append(x)
     logits = linear(norm_one_plus(x, w["final.norm"], eps), w["head"])
     return (logits, np.stack(after)) if return_layers else logits
@@ -239,13 +241,14 @@ def random_config(rng, layer_types=("lightning", "attention", "retention"), widt
                 vocab=vocab, width=width)
 
 
-def tensor_shapes(cfg):
-    """name -> shape of every tensor of a configuration, in file order."""
+def tensor_shapes(cfg, norm2_always=False):
+    """name -> shape of every tensor of a configuration, in file order.  norm2_always: also for layers
+    without a feed-forward."""
     D, out = cfg["width"], {"embed": (cfg["vocab"], cfg["width"])}
     for i, layer in enumerate(cfg["layers"]):
         m, p = layer["mixer"], f"l{i}."
         out[p + "norm1"] = (D,)
-        if layer.get("mlp") is not None:
+        if layer.get("mlp") is not None or norm2_always:
             out[p + "norm2"] = (D,)
         H, d, dv = m["heads"], m["dim"], m["vdim"]
         if layer["type"] == "attention":

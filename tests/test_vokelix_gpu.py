@@ -28,11 +28,11 @@ def to_bf16_bits(a):
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
-def write_model(folder, cfg, seed, sink_scale=2.0):
+def write_model(folder, cfg, seed, sink_scale=2.0, norm2_always=False):
     """config.json + model.safetensors (bfloat16) with random weights; returns the float64 weights."""
     rng = np.random.default_rng(seed)
     w, blobs, header, off = {}, [], {}, 0
-    for name, shape in pv.tensor_shapes(cfg).items():
+    for name, shape in pv.tensor_shapes(cfg, norm2_always).items():
         fan_in = shape[-1]
         if name.endswith(".sink"):
             a = rng.normal(0, sink_scale, shape)
@@ -154,6 +154,18 @@ def test_each_mechanism_alone(which, dtype, tmp_path):
     ref = pv.forward(cfg, w, ids)
     eng = engine(str(tmp_path), dtype, max_seq_len=256)
     assert_close(whole(eng, ids), ref, dtype, which)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_second_norm_of_a_layer_without_feed_forward(dtype, tmp_path):
+    """A weight file may hold a second norm for a layer that has no feed-forward: it then norms the scaled
+    stream alone.  (Without the tensor the layer ends after its first norm: `no_feed_forward` above.)"""
+    cfg = with_max_positions(pv.random_config(np.random.default_rng(1), ("lightning", "attention"), no_mlp=[0, 1]), 256)
+    w = write_model(str(tmp_path), cfg, 3, norm2_always=True)
+    assert "l0.norm2" in w
+    ids = prompt(cfg, 70, 5)
+    eng = engine(str(tmp_path), dtype, max_seq_len=256)
+    assert_close(in_portions(eng, ids, [66, 1]), pv.forward(cfg, w, ids), dtype, "second norm without feed-forward")
 
 
 # ------------------------------------------------------------------ whole models, every way of cutting
