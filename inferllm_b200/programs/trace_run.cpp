@@ -15,9 +15,10 @@
 //
 // It samples nothing and has no forward pass, cache or loader of its own: it drives illm::Engine::step,
 // the function that generation uses.  --max-tokens is the number of tokens that live requests hold at
-// any time, each request rounded up to a multiple of the page size (64); it sizes the cache.
+// any time; it sizes the cache (with a page of slack for each of up to 256 live requests).
 #include <sys/stat.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 #include <iostream>
@@ -61,7 +62,11 @@ static int run(int argc, char** argv) {
     EngineOptions opt;
     opt.dtype = dtype;
     opt.device_id = device;
-    opt.max_tokens = max_tokens;
+    // --max-tokens counts the tokens themselves; a request holds whole pages, so up to 256 live requests get a page of
+    // slack each, and as many slots (per-sequence state is per slot, so their number is bounded too)
+    const long long slack = std::min<long long>(256, max_tokens);
+    opt.max_tokens = max_tokens + slack * opt.page_size;
+    opt.max_batch = (int)std::min<long long>(256, (opt.max_tokens + opt.page_size - 1) / opt.page_size);
     // no request can be longer than what all live requests hold together (whole pages)
     opt.max_seq_len = (max_tokens + opt.page_size - 1) / opt.page_size * opt.page_size;
     std::unique_ptr<Engine> engine = Engine::from_folder(model, opt);
