@@ -1,8 +1,8 @@
 // Causal attention of every token of a step over the paged cache: the generic kernel.
 //
-// It takes any head size that is a multiple of 8 up to 256, any number of heads and groups,
-// any page size, float32 or bfloat16 storage, prompts and single tokens alike, and does all
-// arithmetic in float32.  It is the whole attention of the float32 mode and the fall-back of
+// It takes any head size up to 256 (16-byte loads where it is a multiple of 8, element by element
+// otherwise), any number of heads and groups, any page size, float32 or bfloat16 storage, prompts
+// and single tokens alike, and does all arithmetic in float32.  It is the whole attention of the float32 mode and the fall-back of
 // the bfloat16 mode for head sizes that the tensor-core kernels do not take.
 //
 // The reference materialises the score matrix and runs four launches over it: a batched
