@@ -375,11 +375,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(DecayScanArgs a)
     }
 }
 
-// head sizes up to 1024
-extern "C" long long illm_decay_scan_smem(int d, int dv) {
-    (void)dv;
-    return d <= 1024 ? 40 * 1024 : (1LL << 40);
-}
+// head sizes up to 1024 (the rows of a column group over at most 32 lanes), any value size
+extern "C" int illm_decay_scan_supported(int d, int dv) { return d > 0 && d <= 1024 && dv > 0 ? 1 : 0; }
 
 template <int R, int C, int LI>
 static void decay_launch(DecayScanArgs a, int B, cudaStream_t s) {

@@ -33,7 +33,7 @@ int illm_attention_prefill(const void* q, int q_stride, const void* kc, const vo
 int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, int* err, void* stream);
 
 // decay_state.cu
-long long illm_decay_scan_smem(int d, int dv);
+int illm_decay_scan_supported(int d, int dv);
 int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, int segments, float* seg_state, void* stream);
 int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
 

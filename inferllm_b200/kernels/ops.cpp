@@ -431,7 +431,7 @@ Mat qk_prep(Device& dev, const Mat& x, const QkPrep& p, Geometry g, const StepVi
     return q;
 }
 
-bool decay_scan_supported(int d, int dv) { return d > 0 && dv > 0 && illm_decay_scan_smem(d, dv) <= 220 * 1024; }      // head sizes up to 1024
+bool decay_scan_supported(int d, int dv) { return illm_decay_scan_supported(d, dv) != 0; }      // head sizes up to 1024
 
 int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms) {
     const long long blocks = (long long)B * n_heads * ceil_div(v_head_dim, 64);      // a block covers 64 columns of a head

@@ -64,7 +64,7 @@ struct DecayLinearAttention : Mixer {
             for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
         if (rt && !ops::decay_scan_supported(head_dim, v_head_dim))
             throw ConfigError("decay_linear_attention: a state of " + std::to_string(head_dim) + " x " + std::to_string(v_head_dim) +
-                              " per head is larger than the kernel's shared memory holds");
+                              " per head is beyond the kernel (head sizes up to 1024)");
         position = build_position(s.has("position") ? s.get_part("position") : PartSpec("none", Json::object()), rt);
         if (rt) position->prepare();
     }
