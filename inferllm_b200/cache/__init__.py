@@ -16,14 +16,19 @@ from ..binding import CacheError, CacheFull   # noqa: F401
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every position (or of the last `window` positions) of a sequence."""
+    """Keys and values of every position (or of the last `window` positions) of a sequence; `keys_only`: one row
+    per position that serves as key and as value (a shared latent), no value pages."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keys_only: bool = False
 
     def to_json(self):
-        return {"kind": "kv", "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "window": self.window}
+        j = {"kind": "kv", "n_kv_heads": self.n_kv_heads, "head_dim": self.head_dim, "window": self.window}
+        if self.keys_only:
+            j["keys_only"] = True
+        return j
 
 
 @dataclass(frozen=True)

@@ -19,6 +19,11 @@ CacheRequest CacheRequest::paged(int n_kv_heads, int head_dim, int window, int v
     r.v_head_dim = v_head_dim > 0 ? v_head_dim : head_dim;
     return r;
 }
+CacheRequest CacheRequest::paged_keys_only(int n_kv_heads, int head_dim, int window) {
+    CacheRequest r = paged(n_kv_heads, head_dim, window, head_dim);
+    r.keys_only = true;
+    return r;
+}
 CacheRequest CacheRequest::state(std::vector<long long> shape, DType dtype) {
     CacheRequest r;
     r.kind = FixedState;
@@ -28,7 +33,7 @@ CacheRequest CacheRequest::state(std::vector<long long> shape, DType dtype) {
 }
 bool CacheRequest::operator==(const CacheRequest& o) const {
     return kind == o.kind && n_kv_heads == o.n_kv_heads && head_dim == o.head_dim && v_head_dim == o.v_head_dim && window == o.window &&
-           shape == o.shape &&
+           keys_only == o.keys_only && shape == o.shape &&
            (kind != FixedState || dtype == o.dtype);
 }
 Json CacheRequest::to_json() const {
@@ -39,6 +44,7 @@ Json CacheRequest::to_json() const {
         j.set("n_kv_heads", n_kv_heads);
         j.set("head_dim", head_dim);
         if (v_head_dim != head_dim) j.set("v_head_dim", v_head_dim);
+        if (keys_only) j.set("keys_only", true);
         j.set("window", window ? Json(window) : Json());
     } else {
         j.set("kind", "state");
@@ -52,6 +58,9 @@ Json CacheRequest::to_json() const {
 CacheRequest CacheRequest::from_json(const Json& j) {
     if (j.is_null()) return CacheRequest();
     const std::string kind = j.at("kind").is_string() ? j.at("kind").as_string() : "";
+    if (kind == "kv" && j.has("keys_only") && j.at("keys_only").is_bool() && j.at("keys_only").as_bool())
+        return paged_keys_only((int)j.at("n_kv_heads").as_int(), (int)j.at("head_dim").as_int(),
+                               j.at("window").is_int() ? (int)j.at("window").as_int() : 0);
     if (kind == "kv")
         return paged((int)j.at("n_kv_heads").as_int(), (int)j.at("head_dim").as_int(),
                      j.at("window").is_int() ? (int)j.at("window").as_int() : 0,
@@ -182,7 +191,7 @@ size_t SequenceCache::bytes_per_token(const std::map<int, CacheRequest>& request
     size_t n = 0;
     for (auto& r : requests)
         if (r.second.kind == CacheRequest::PagedKV)
-            n += (size_t)r.second.n_kv_heads * (r.second.head_dim + r.second.v_head_dim) * dtype_size(dtype);
+            n += (size_t)r.second.n_kv_heads * (r.second.head_dim + (r.second.keys_only ? 0 : r.second.v_head_dim)) * dtype_size(dtype);
     return n;
 }
 
@@ -226,7 +235,7 @@ SequenceCache::SequenceCache(const std::map<int, CacheRequest>& requests, int nu
     for (PagedGroup& g : paged) {
         g.page_bytes = (size_t)g.request.n_kv_heads * page_size * g.request.head_dim * dtype_size(dtype);
         g.entry_bytes = g.page_bytes * num_pages;
-        g.v_page_bytes = (size_t)g.request.n_kv_heads * page_size * g.request.v_head_dim * dtype_size(dtype);
+        g.v_page_bytes = g.request.keys_only ? 0 : (size_t)g.request.n_kv_heads * page_size * g.request.v_head_dim * dtype_size(dtype);
         g.v_entry_bytes = g.v_page_bytes * num_pages;
     }
     for (StateGroup& g : states) g.entry_bytes = (size_t)num_slots * g.request.elements() * dtype_size(g.request.dtype);
@@ -241,10 +250,10 @@ SequenceCache::SequenceCache(const std::map<int, CacheRequest>& requests, int nu
     }
     for (PagedGroup& g : paged) {
         g.k = device_->alloc_persistent(g.entry_bytes * g.entries.size(), "the cache's keys", !poison);
-        g.v = device_->alloc_persistent(g.v_entry_bytes * g.entries.size(), "the cache's values", !poison);
+        if (g.v_entry_bytes) g.v = device_->alloc_persistent(g.v_entry_bytes * g.entries.size(), "the cache's values", !poison);
         if (poison) {
             check_cuda(cudaMemsetAsync(g.k, 0xFF, g.entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
-            check_cuda(cudaMemsetAsync(g.v, 0xFF, g.v_entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
+            if (g.v) check_cuda(cudaMemsetAsync(g.v, 0xFF, g.v_entry_bytes * g.entries.size(), device_->stream()), "poisoning the cache");
         }
     }
     for (StateGroup& g : states) g.state = device_->alloc_persistent(g.entry_bytes * g.entries.size(), "the per-sequence state", true);
@@ -254,7 +263,7 @@ SequenceCache::~SequenceCache() {
     if (!device_) return;
     for (PagedGroup& g : paged) {
         device_->free_persistent(g.k);
-        device_->free_persistent(g.v);
+        if (g.v) device_->free_persistent(g.v);
     }
     for (StateGroup& g : states) device_->free_persistent(g.state);
     device_->free_persistent(poison_list_);
@@ -274,7 +283,11 @@ void SequenceCache::poison_pages(PagedGroup& g, const std::vector<int>& pages) {
     std::copy(pages.begin(), pages.end(), poison_host_);
     check_cuda(cudaMemcpyAsync(poison_list_, poison_host_, pages.size() * 4, cudaMemcpyHostToDevice, device_->stream()),
                "uploading the pages to poison");
-    if (g.v_page_bytes == g.page_bytes) {
+    if (!g.v) {        // keys only
+        check_kernel(illm_poison_pages(g.k, g.k, (long long)g.entry_bytes, (int)g.entries.size(), (long long)g.page_bytes, poison_list_,
+                                       (int)pages.size(), device_->stream()),
+                     "poison_pages");
+    } else if (g.v_page_bytes == g.page_bytes) {
         check_kernel(illm_poison_pages(g.k, g.v, (long long)g.entry_bytes, (int)g.entries.size(), (long long)g.page_bytes, poison_list_,
                                        (int)pages.size(), device_->stream()),
                      "poison_pages");
@@ -387,7 +400,7 @@ KVView SequenceCache::kv_view(int entry, const int* table_dev) const {
     const PagedGroup& g = paged[it->second.group];
     KVView v;
     v.k = g.k ? (char*)g.k + (size_t)it->second.index * g.entry_bytes : nullptr;
-    v.v = g.v ? (char*)g.v + (size_t)it->second.index * g.v_entry_bytes : nullptr;
+    v.v = g.request.keys_only ? v.k : g.v ? (char*)g.v + (size_t)it->second.index * g.v_entry_bytes : nullptr;
     v.block_table = table_dev;
     v.width = width;
     v.num_pages = num_pages;

@@ -37,11 +37,15 @@ struct CacheRequest {
     // PagedKV: keys and values of every position (window 0) or of the last `window` positions
     // (value rows of v_head_dim elements; equal to head_dim unless the mixer says otherwise)
     int n_kv_heads = 0, head_dim = 0, window = 0, v_head_dim = 0;
+    // PagedKV with keys_only: one row per position that serves as key and as value (a shared latent); no value
+    // pages are kept, and a view's `v` is its `k`
+    bool keys_only = false;
     // FixedState: `elements` values of `dtype` per sequence, zeroed when a slot is handed out
     std::vector<long long> shape;
     DType dtype = DType::F32;
 
     static CacheRequest paged(int n_kv_heads, int head_dim, int window = 0, int v_head_dim = 0);
+    static CacheRequest paged_keys_only(int n_kv_heads, int head_dim, int window = 0);
     static CacheRequest state(std::vector<long long> shape, DType dtype = DType::F32);
     long long elements() const { long long n = 1; for (long long s : shape) n *= s; return n; }
     bool operator==(const CacheRequest& o) const;

@@ -60,11 +60,13 @@ class LayerSpec:
 @dataclass
 class ScheduleEntry:
     """One execution of a layer: `layer` indexes ModelSpec.layers, `cache` numbers the cache entry the
-    mixer uses, `writes=False` only reads what an earlier entry of the same step wrote."""
+    mixer uses, `writes=False` only reads what an earlier entry of the same step wrote, `reenter=True` replaces
+    the stream by the model's re-entry map of [stream; embedding output] before the layer runs."""
 
     layer: int
     cache: int
     writes: bool = True
+    reenter: bool = False
 
 
 @dataclass
@@ -79,15 +81,18 @@ class ModelSpec:
     max_positions: int
     bos_token_id: Optional[int]
     eos_token_ids: List[int]
+    reentry: Optional[PartSpec] = None      # a feed-forward part [2 hidden -> hidden] for the entries marked `reenter`
 
     def to_json(self):
-        return {"hidden_size": self.hidden_size, "vocab_size": self.vocab_size, "max_positions": self.max_positions,
+        extra = {"reentry": self.reentry.to_json()} if self.reentry is not None else {}
+        return {**extra, "hidden_size": self.hidden_size, "vocab_size": self.vocab_size, "max_positions": self.max_positions,
                 "bos_token_id": self.bos_token_id, "eos_token_ids": list(self.eos_token_ids),
                 "embedding": self.embedding.to_json(), "final_norm": self.final_norm.to_json(), "head": self.head.to_json(),
                 "layers": [{"block": ls.block, "mixer": ls.mixer.to_json(), "ffn": ls.ffn.to_json(),
                             "norms": {r: n.to_json() for r, n in ls.norms.items()}, "prefix": ls.prefix,
                             "names": dict(ls.names)} for ls in self.layers],
-                "schedule": [{"layer": e.layer, "cache": e.cache, "writes": e.writes} for e in self.schedule]}
+                "schedule": [{"layer": e.layer, "cache": e.cache, "writes": e.writes, **({"reenter": True} if e.reenter else {})}
+                             for e in self.schedule]}
 
     @staticmethod
     def from_json(j):
@@ -95,9 +100,10 @@ class ModelSpec:
                             {r: PartSpec.from_json(n) for r, n in ls["norms"].items()}, ls["prefix"], dict(ls["names"]))
                   for ls in j["layers"]]
         return ModelSpec(j["hidden_size"], j["vocab_size"], layers,
-                         [ScheduleEntry(e["layer"], e["cache"], e.get("writes", True)) for e in j["schedule"]],
+                         [ScheduleEntry(e["layer"], e["cache"], e.get("writes", True), e.get("reenter", False)) for e in j["schedule"]],
                          PartSpec.from_json(j["embedding"]), PartSpec.from_json(j["final_norm"]), PartSpec.from_json(j["head"]),
-                         j["max_positions"], j.get("bos_token_id"), list(j.get("eos_token_ids", [])))
+                         j["max_positions"], j.get("bos_token_id"), list(j.get("eos_token_ids", [])),
+                         PartSpec.from_json(j["reentry"]) if j.get("reentry") else None)
 
     def validate(self):
         """ConfigError for a schedule that names no layer, writes an entry twice or reads before writing."""
@@ -200,7 +206,16 @@ class VokelixConfig(LibraryConfig):
     architecture = "Vokelix"
 
 
-_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig}
+class VizosunConfig(LibraryConfig):
+    """The Vizosun decoder (`config/vizosun.h`): `layers` (a list of {type: "channel_delta" | "latent_attention",
+    mixer: {...}, mlp: {kind: "dense", ff} | {kind: "moe", expert: {ff}, router: {experts, top}} | None}), `width`,
+    `vocab`, `norm` ({eps}), optionally `embedding` ({bigram: {buckets, mul_prev, mul_cur}}), `loop` ({start, stop,
+    times}) and `max_positions`.  The dictionary names the class under `architecture`."""
+
+    architecture = "Vizosun"
+
+
+_PY_CLASSES: Dict[str, type] = {"LlamaForCausalLM": LlamaConfig, "Vokelix": VokelixConfig, "Vizosun": VizosunConfig}
 _CALLBACKS = {}      # name -> (ctypes callback, holder of the last returned text): kept alive while registered
 
 
@@ -243,7 +258,7 @@ def register_architecture(name: str, config_cls: type, aliases=()):
 def unregister_architecture(name: str):
     _b.check(_b.lib().illm_unregister_architecture(name.encode()))
     _CALLBACKS.pop(name, None)
-    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig):
+    if _PY_CLASSES.get(name) not in (LlamaConfig, VokelixConfig, VizosunConfig):
         _PY_CLASSES.pop(name, None)
 
 

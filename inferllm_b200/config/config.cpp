@@ -68,6 +68,8 @@ void ModelSpec::validate() const {
                 throw ConfigError("schedule entries " + std::to_string(it->second) + " and " + std::to_string(i) +
                                   " both write cache entry " + std::to_string(e.cache));
             writer[e.cache] = i;
+            if (e.reenter && reentry.kind.empty())
+                throw ConfigError("schedule entry " + std::to_string(i) + " re-enters the stream, but the model has no re-entry map");
         } else if (!writer.count(e.cache)) {
             throw ConfigError("schedule entry " + std::to_string(i) + " reads cache entry " + std::to_string(e.cache) +
                               " before any entry has written it");
@@ -109,9 +111,11 @@ Json ModelSpec::to_json() const {
         o.set("layer", e.layer);
         o.set("cache", e.cache);
         o.set("writes", e.writes);
+        if (e.reenter) o.set("reenter", true);
         sch.push(o);
     }
     j.set("schedule", sch);
+    if (!reentry.kind.empty()) j.set("reentry", reentry.to_json());
     return j;
 }
 
@@ -148,8 +152,10 @@ ModelSpec ModelSpec::from_json(const Json& j) {
         e.layer = (int)take_int(o, "layer");
         e.cache = (int)take_int(o, "cache");
         e.writes = take_bool(o, "writes", true);
+        e.reenter = take_bool(o, "reenter", false);
         s.schedule.push_back(e);
     }
+    if (j.has("reentry") && j.at("reentry").is_object()) s.reentry = PartSpec::from_json(j.at("reentry"), "model spec, reentry");
     return s;
 }
 
@@ -205,6 +211,7 @@ Registry& registry() {
 
 void register_llama_architecture();     // config/llama.cpp
 void register_vokelix_architecture();   // config/vokelix.cpp
+void register_vizosun_architecture();   // config/vizosun.cpp
 
 static void ensure_builtin() {
     static bool done = false;
@@ -212,6 +219,7 @@ static void ensure_builtin() {
         done = true;
         register_llama_architecture();
         register_vokelix_architecture();
+        register_vizosun_architecture();
     }
 }
 

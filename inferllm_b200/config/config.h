@@ -63,9 +63,12 @@ struct LayerSpec {
 // the mixer uses: an entry with writes == true owns it and appends to it; one with writes == false
 // only reads what an earlier entry of the same step wrote (a layer attending to another layer's
 // keys and values).
+// `reenter`: before the layer runs, the stream is replaced by the model's re-entry map of [stream; embedding
+// output] (ModelSpec::reentry), as a model does that runs some of its layers several times in a row.
 struct ScheduleEntry {
     int layer = 0, cache = 0;
     bool writes = true;
+    bool reenter = false;
 };
 
 struct ModelSpec {
@@ -75,6 +78,9 @@ struct ModelSpec {
     PartSpec embedding;    // params: name (tensor-name prefix), vocab_size, hidden_size, ...
     PartSpec final_norm;   // params: name, size, eps, ...
     PartSpec head;         // params: name, tied, vocab_size, hidden_size, ...
+    // A feed-forward part [2 hidden -> hidden] (kind "" = none) applied to the stream joined with the embedding
+    // output before every schedule entry marked `reenter`; params: name (tensor-name prefix), ...
+    PartSpec reentry;
     bool has_bos = false;
     long long bos_token_id = 0;
     std::vector<long long> eos_token_ids;

@@ -422,10 +422,11 @@ extern "C" int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, in
     return illm_launch_status();
 }
 
-// y[t, g, :] = o[t, g, :] / sqrt(mean_g(o^2) + eps) (* w) * act(gate[t, g, :]);  one block per (token, group)
+// y[t, g, :] = o[t, g, :] / sqrt(mean_g(o^2) + eps) (* w) * act(gate[t, g, :]);  one block per (token, group);
+// w covers the whole row or, shorter, repeats along it
 template <typename TA>
 __global__ void __launch_bounds__(128)
-group_norm_gate_kernel(const float* __restrict__ o, int width, int group, const float* __restrict__ w, float eps,
+group_norm_gate_kernel(const float* __restrict__ o, int width, int group, const float* __restrict__ w, int w_len, float eps,
                        const float* __restrict__ gate, int gate_ld, int gate_act, TA* __restrict__ y) {
     pdl_grid_sync();
     __shared__ float scratch[32];
@@ -437,22 +438,25 @@ group_norm_gate_kernel(const float* __restrict__ o, int width, int group, const 
     const float inv = 1.0f / sqrtf(ss / (float)group + eps);
     for (int c = threadIdx.x; c < group; c += blockDim.x) {
         float v = row[c] * inv;
-        if (w) v *= w[g0 + c];
+        if (w) v *= w[(g0 + c) % w_len];
         if (gate) v *= act_of(gate[(size_t)t * gate_ld + g0 + c], gate_act);
         y[(size_t)t * width + g0 + c] = from_f32<TA>(v);
     }
 }
 
-extern "C" int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, float eps, const float* gate, int gate_ld,
-                                    int gate_act, void* y, int act_dtype, void* stream) {
+// w_len: the weight's length, the whole width or a divisor of it (a weight of one group's size is shared by the groups)
+extern "C" int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate,
+                                    int gate_ld, int gate_act, void* y, int act_dtype, void* stream) {
     if (T <= 0) return 0;
     if (width <= 0 || group <= 0 || width % group || width / group > 65535 || !o || !y) return ILLM_ERR_BAD_ARG;
+    if (w && (w_len <= 0 || width % w_len)) return ILLM_ERR_BAD_ARG;
+    if (!w) w_len = width;
     dim3 grid(T, width / group);
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == ILLM_BF16)
-        illm_launch(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, s, o, width, group, w, eps, gate, gate_ld, gate_act, (bf16*)y);
+        illm_launch(group_norm_gate_kernel<bf16>, grid, dim3(128), 0, s, o, width, group, w, w_len, eps, gate, gate_ld, gate_act, (bf16*)y);
     else if (act_dtype == ILLM_F32)
-        illm_launch(group_norm_gate_kernel<float>, grid, dim3(128), 0, s, o, width, group, w, eps, gate, gate_ld, gate_act, (float*)y);
+        illm_launch(group_norm_gate_kernel<float>, grid, dim3(128), 0, s, o, width, group, w, w_len, eps, gate, gate_ld, gate_act, (float*)y);
     else
         return ILLM_ERR_BAD_ARG;
     return illm_launch_status();

@@ -1,0 +1,240 @@
+// The gated delta rule with a decay per head and key channel, over per-sequence state.
+//
+// Per head, with the state S [d, dv] float32 (zero when a sequence starts), for every token in order:
+//     S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+// so the read-out sees the token's own write.  Before that, per token (delta_prep_kernel):
+//     q, k, v  = silu(conv(projection))     a causal convolution over time per channel, `taps` wide, the last
+//                                           tap the token's own, zeros before the sequence's start
+//     q, k     = x / sqrt(sum(x^2) + 1e-6) per head;  q also times q_scale
+//     beta     = sigmoid(b)                 one per head
+//     g        = exp(-exp(A_log_h) * softplus(a + dt_bias))      one per head and key channel
+// Query/key head of value head h: h / (heads / kv_heads).  The last taps - 1 rows of the raw q, k, v projections
+// are per-sequence state as well ([taps - 1, channels] behind S in a slot's row), renewed by conv_state_kernel
+// after the preparation has read them.  Everything here is float32 in both modes of the engine.
+//
+// delta_scan_kernel: the columns of S never meet, so a block owns (sequence, head, a group of columns); a column's
+// d rows are spread over L lanes (L the smallest power of two that leaves a thread at most 32 rows) and live in
+// registers for the whole step.  The step's tokens are staged through shared memory in tiles.  The two dot
+// products of a token are added over the L lanes by a fixed tree of shuffles, and a token's arithmetic does not
+// depend on where the step's cut falls, so prompts, portions and single tokens give the same bits.
+#include "common.cuh"
+
+#define DL_THREADS 128
+#define DL_ROWS 32
+#define DL_TILE 16
+
+struct DeltaArgs {
+    const float* x;                 // [T, ld] the packed float32 projection
+    int ld, q_off, k_off, v_off, b_off;
+    const float* a;                 // [T, nh * d] decay projection (before the bias)
+    int nh, nkv, d, dv, taps;
+    const float *conv_q, *conv_k, *conv_v;      // [channels, taps]
+    const float *a_log, *dt_bias;               // [nh], [nh * d]
+    float q_scale;
+    float* state;                   // [slots, state_elems]: S [nh, dv, d], then the convolution's rows [taps - 1, C]
+    long long state_elems;
+    const int *slots, *cu_q, *token_pos, *token_seq, *seq_lens;
+    float* qkv;                     // out [T, C] prepared q, k, v (C = 2 nkv d + nh dv)
+    float* g;                       // out [T, nh * d]
+    float* beta;                    // out [T, nh]
+    float* out;                     // [T, nh * dv]
+};
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+// one block per token; dynamic shared memory: C floats
+__global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
+    pdl_grid_sync();
+    extern __shared__ float sm[];
+    const int t = blockIdx.x;
+    const int seq = p.token_seq[t], pos = p.token_pos[t];
+    const int first = p.cu_q[seq];                 // the step's first token of this sequence
+    const int i_step = t - first;
+    const int nq = p.nkv * p.d, nv = p.nh * p.dv, C = 2 * nq + nv, K = p.taps;
+    const float* conv_state = p.state + (size_t)p.slots[seq] * p.state_elems + (size_t)p.nh * p.d * p.dv;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float* taps;
+        int col;
+        if (c < nq) { taps = p.conv_q + (size_t)c * K; col = p.q_off + c; }
+        else if (c < 2 * nq) { taps = p.conv_k + (size_t)(c - nq) * K; col = p.k_off + c - nq; }
+        else { taps = p.conv_v + (size_t)(c - 2 * nq) * K; col = p.v_off + c - 2 * nq; }
+        float y = 0.f;
+        for (int j = K - 1; j >= 0; j--) {          // oldest input first
+            if (pos - j < 0) continue;
+            const float in = j <= i_step ? p.x[(size_t)(t - j) * p.ld + col] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
+            y = fmaf(taps[K - 1 - j], in, y);
+        }
+        sm[c] = silu_f(y);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    float* dst = p.qkv + (size_t)t * C;
+    for (int hh = warp; hh < 2 * p.nkv; hh += n_warps) {          // unit vectors per query and key head
+        const float* v = sm + (size_t)hh * p.d;
+        float ss = 0.f;
+        for (int i = lane; i < p.d; i += 32) ss = fmaf(v[i], v[i], ss);
+        ss = warp_sum(ss);
+        const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (hh < p.nkv ? p.q_scale : 1.0f);
+        for (int i = lane; i < p.d; i += 32) dst[(size_t)hh * p.d + i] = v[i] * inv;
+    }
+    for (int c = threadIdx.x; c < nv; c += blockDim.x) dst[2 * nq + c] = sm[2 * nq + c];
+    for (int c = threadIdx.x; c < p.nh * p.d; c += blockDim.x) {
+        const int h = c / p.d;
+        const float z = p.a[(size_t)t * p.nh * p.d + c] + p.dt_bias[c];
+        const float sp = z > 20.f ? z : log1pf(expf(z));
+        p.g[(size_t)t * p.nh * p.d + c] = expf(-expf(p.a_log[h]) * sp);
+    }
+    for (int h = threadIdx.x; h < p.nh; h += blockDim.x) p.beta[(size_t)t * p.nh + h] = 1.0f / (1.0f + expf(-p.x[(size_t)t * p.ld + p.b_off + h]));
+}
+
+// The convolution's rows after the step: the raw projections of the sequence's last taps - 1 positions (zeros for
+// positions before its start).  A thread owns a channel and goes through the rows in ascending order, so that a
+// row kept from before the step is read before it is overwritten.
+__global__ void conv_state_kernel(DeltaArgs p) {
+    pdl_grid_sync();
+    const int b = blockIdx.y;
+    const int nq = p.nkv * p.d, nv = p.nh * p.dv, C = 2 * nq + nv, K = p.taps;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int col = c < nq ? p.q_off + c : c < 2 * nq ? p.k_off + c - nq : p.v_off + c - 2 * nq;
+    const int first = p.cu_q[b], n = p.cu_q[b + 1] - first;
+    const int len = p.seq_lens[b], past = len - n;
+    float* cs = p.state + (size_t)p.slots[b] * p.state_elems + (size_t)p.nh * p.d * p.dv;
+    for (int r = 0; r < K - 1; r++) {
+        const int pos = len - (K - 1) + r;
+        float v = 0.f;
+        if (pos >= past) v = p.x[(size_t)(first + pos - past) * p.ld + col];
+        else if (pos >= 0) v = cs[(size_t)(r + n) * C + c];
+        cs[(size_t)r * C + c] = v;
+    }
+}
+
+// grid (column groups, heads, sequences); L lanes per column, DL_THREADS / L columns per block
+template <int L>
+__global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
+    pdl_grid_sync();
+    extern __shared__ float sm[];
+    constexpr int COLS = DL_THREADS / L;
+    const int b = blockIdx.z, h = blockIdx.y, hk = h / (p.nh / p.nkv);
+    const int d = p.d, dv = p.dv;
+    const int l = threadIdx.x % L, jc = threadIdx.x / L;
+    const int j = blockIdx.x * COLS + jc;           // the thread's column
+    const bool live = j < dv;
+    const int first = p.cu_q[b], n = p.cu_q[b + 1] - first;
+    const int nq = p.nkv * d, C = 2 * nq + p.nh * dv;
+    float* S_col = p.state + (size_t)p.slots[b] * p.state_elems + ((size_t)h * dv + (live ? j : 0)) * d;
+    float S[DL_ROWS];
+#pragma unroll
+    for (int r = 0; r < DL_ROWS; r++) {
+        const int i = l + L * r;
+        S[r] = (live && i < d) ? S_col[i] : 0.f;
+    }
+    // a tile of tokens in shared memory: q, k, g [tile, d] each, v [tile, COLS], beta [tile]
+    float* sq = sm;
+    float* sk = sq + DL_TILE * d;
+    float* sg = sk + DL_TILE * d;
+    float* sv = sg + DL_TILE * d;
+    float* sb = sv + DL_TILE * COLS;
+    const int j0 = blockIdx.x * COLS;
+    for (int t0 = 0; t0 < n; t0 += DL_TILE) {
+        const int nt = min(DL_TILE, n - t0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * d; e += DL_THREADS) {
+            const int tt = e / d, i = e - tt * d;
+            const size_t t = (size_t)(first + t0 + tt);
+            sq[e] = p.qkv[t * C + (size_t)hk * d + i];
+            sk[e] = p.qkv[t * C + nq + (size_t)hk * d + i];
+            sg[e] = p.g[t * p.nh * d + (size_t)h * d + i];
+        }
+        for (int e = threadIdx.x; e < nt * COLS; e += DL_THREADS) {
+            const int tt = e / COLS, c = e - tt * COLS;
+            sv[e] = j0 + c < dv ? p.qkv[(size_t)(first + t0 + tt) * C + 2 * nq + (size_t)h * dv + j0 + c] : 0.f;
+        }
+        for (int e = threadIdx.x; e < nt; e += DL_THREADS) sb[e] = p.beta[(size_t)(first + t0 + e) * p.nh + h];
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float *q = sq + tt * d, *k = sk + tt * d, *g = sg + tt * d;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < DL_ROWS; r++) {
+                const int i = l + L * r;
+                if (i < d) {
+                    S[r] *= g[i];
+                    acc = fmaf(k[i], S[r], acc);
+                }
+            }
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            const float u = sb[tt] * (sv[tt * COLS + jc] - acc);
+            float oacc = 0.f;
+#pragma unroll
+            for (int r = 0; r < DL_ROWS; r++) {
+                const int i = l + L * r;
+                if (i < d) {
+                    S[r] = fmaf(k[i], u, S[r]);
+                    oacc = fmaf(q[i], S[r], oacc);
+                }
+            }
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, o);
+            if (live && l == 0) p.out[(size_t)(first + t0 + tt) * p.nh * dv + (size_t)h * dv + j] = oacc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < DL_ROWS; r++) {
+            const int i = l + L * r;
+            if (i < d) S_col[i] = S[r];
+        }
+    }
+}
+
+extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 1 && d <= 32 * DL_ROWS && dv >= 1 && taps >= 1 && taps <= 64; }
+
+template <int L>
+static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
+    constexpr int COLS = DL_THREADS / L;
+    const size_t smem = (size_t)(DL_TILE * (3 * p.d + COLS + 1)) * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(delta_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    illm_launch(delta_scan_kernel<L>, dim3((p.dv + COLS - 1) / COLS, p.nh, B), dim3(DL_THREADS), smem, s, p);
+}
+
+// x: [T, ld] float32 with q at q_off (nkv * d columns), k at k_off, v at v_off (nh * dv), beta's logits at b_off (nh).
+// state: float32 [slots, state_elems], state_elems >= nh * d * dv + (taps - 1) * (2 nkv d + nh dv).
+// Scratch qkv [T, 2 nkv d + nh dv], g [T, nh d], beta [T, nh]; out [T, nh dv].
+extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_off, int v_off, int b_off, const float* a, int nh, int nkv, int d,
+                               int dv, int taps, const float* conv_q, const float* conv_k, const float* conv_v, const float* a_log,
+                               const float* dt_bias, float q_scale, float* state, long long state_elems, const int* slots, const int* cu_q,
+                               const int* token_pos, const int* token_seq, const int* seq_lens, float* qkv, float* g, float* beta, float* out,
+                               int B, void* stream) {
+    if (T <= 0 || B <= 0) return 0;
+    if (!illm_delta_rule_supported(d, dv, taps) || nkv <= 0 || nh % nkv) return ILLM_ERR_BAD_ARG;
+    const long long C = 2LL * nkv * d + (long long)nh * dv;
+    if (state_elems < (long long)nh * d * dv + (taps - 1) * C) return ILLM_ERR_BAD_ARG;
+    if (C * sizeof(float) > 200 * 1024 || (size_t)(DL_TILE * (3 * d + DL_THREADS + 1)) * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    DeltaArgs p;
+    p.x = x; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off;
+    p.a = a; p.nh = nh; p.nkv = nkv; p.d = d; p.dv = dv; p.taps = taps;
+    p.conv_q = conv_q; p.conv_k = conv_k; p.conv_v = conv_v; p.a_log = a_log; p.dt_bias = dt_bias; p.q_scale = q_scale;
+    p.state = state; p.state_elems = state_elems; p.slots = slots; p.cu_q = cu_q; p.token_pos = token_pos; p.token_seq = token_seq;
+    p.seq_lens = seq_lens; p.qkv = qkv; p.g = g; p.beta = beta; p.out = out;
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    illm_launch(delta_prep_kernel, dim3(T), dim3(256), (size_t)C * sizeof(float), s, p);
+    if (taps > 1) illm_launch(conv_state_kernel, dim3((unsigned)((C + 127) / 128), B), dim3(128), 0, s, p);
+    if (d <= 32) launch_scan<1>(p, B, s);
+    else if (d <= 64) launch_scan<2>(p, B, s);
+    else if (d <= 128) launch_scan<4>(p, B, s);
+    else if (d <= 256) launch_scan<8>(p, B, s);
+    else if (d <= 512) launch_scan<16>(p, B, s);
+    else launch_scan<32>(p, B, s);
+    return illm_launch_status();
+}

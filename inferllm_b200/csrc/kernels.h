@@ -35,9 +35,32 @@ int illm_attention_prefill_tc(const void* q, int q_stride, int T, const void* kc
 // decay_state.cu
 int illm_decay_scan_supported(int d, int dv);
 int illm_decay_scan(float* x, int T, int ld, int q_off, int k_off, int v_off, int nh, int d, int dv, int qk_act, int v_act, const float* cos_sin, int rot, int n_pos, float k_scale, const float* decay, float* state, const int* slots, const int* cu_q, const int* token_pos, float* out, int B, int* err, int segments, float* seg_state, void* stream);
-int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
+int illm_group_norm_gate(const float* o, int T, int width, int group, const float* w, int w_len, float eps, const float* gate, int gate_ld, int gate_act, void* y, int act_dtype, void* stream);
 
 int illm_attention_prefill_tc_ex(const void* q, int q_stride, int T, const void* kc, const void* vc, long long n_pages, const int* block_table, int max_pages, const int* cu_q, const int* seq_lens, void* out, int B, int max_q, int nh, int nkv, int d, int page_size, int window, float scale, int* err, int wide_p, const float* sinks, const float* gate, int gate_stride, void* stream);
+
+// bigram_embedding.cu
+int illm_bigram_embedding(const int* ids, const int* token_pos, const int* token_seq, const int* cu_q, const int* slots, int* last_token, const void* table, const void* bigram, int table_dtype, float* out, int T, int B, int H, int V, int buckets, long long mul_prev, long long mul_cur, int* err, void* stream);
+
+// delta_state.cu
+int illm_delta_rule_supported(int d, int dv, int taps);
+int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_off, int v_off, int b_off, const float* a, int nh, int nkv, int d, int dv, int taps, const float* conv_q, const float* conv_k, const float* conv_v, const float* a_log, const float* dt_bias, float q_scale, float* state, long long state_elems, const int* slots, const int* cu_q, const int* token_pos, const int* token_seq, const int* seq_lens, float* qkv, float* g, float* beta, float* out, int B, void* stream);
+
+// latent_attention.cu
+int illm_latent_prep(const float* x, int ld, int Q, int R, const float* wq, const float* wkv, float eps, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* cq_out, void* kc, int act_dtype, int T, int* err, void* stream);
+int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int T, int heads, int N, int K, int nn, void* stream);
+
+// moe.cu
+int illm_moe_max_tiles(int T, int top, int E, int bm);
+int illm_moe_row_tile(int T, int top);
+int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
+int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
+int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top, void* stream);
+
+// stream_ops.cu
+int illm_gated_act(const void* gu, void* out, int act_dtype, int T, int I, int act, void* stream);
+int illm_take_columns(const float* x, int ld, int off, int n_cols, void* y, int act_dtype, int T, void* stream);
+int illm_join_rows(const float* a, const float* b, int H, void* y, int act_dtype, int T, void* stream);
 
 // embedding.cu
 int illm_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H, int V, int* err, void* stream);

@@ -1,0 +1,143 @@
+// Pieces of attention through low-rank latents.
+//
+// latent_prep_kernel: from a token's packed float32 projection [query latent (Q), key/value latent (R)]:
+//     c_q = rmsnorm(x[0:Q]) * w_q   -> a [T, Q] matrix of the activation dtype (what the query up-projection reads)
+//     c   = rmsnorm(x[Q:Q+R]) * w_kv -> the token's row of the cache's key pages (one head of R channels)
+// Only c is cached: keys and values of every head are linear maps of it, k_h = U_k,h c and v_h = U_v,h c, so
+//     score_h = q_h . (U_k,h c) = (U_k,h^T q_h) . c        and        o_h = U_v,h (sum_j p_j c_j)
+// and attention runs as one shared key/value head of R channels (the cached c is key and value at once) with
+// queries U_k,h^T q_h, followed by U_v,h on its output.  Those two per-head maps are head_gemm_kernel:
+//     y[t, h, :] = W_h x[t, h, :]      (W stored [heads * out, in], "NT")
+//     y[t, h, :] = W_h^T x[t, h, :]    (W stored [heads * in, out], "NN")
+// a 64 x 64 tile per block, float32 accumulation in one chain over the inner index per output, so a row's bits
+// do not depend on what else is in the step.
+#include "common.cuh"
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+latent_prep_kernel(const float* __restrict__ x, int ld, int Q, int R, const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
+                   const int* __restrict__ token_pos, const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_pages,
+                   int page_size, TA* __restrict__ cq_out, TA* __restrict__ kc, int* __restrict__ err) {
+    pdl_grid_sync();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const float* row = x + (size_t)t * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int c = threadIdx.x; c < Q; c += blockDim.x) sq = fmaf(row[c], row[c], sq);
+    for (int c = threadIdx.x; c < R; c += blockDim.x) sk = fmaf(row[Q + c], row[Q + c], sk);
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    const float iq = 1.0f / sqrtf(sq / (float)Q + eps), ik = 1.0f / sqrtf(sk / (float)R + eps);
+    for (int c = threadIdx.x; c < Q; c += blockDim.x) cq_out[(size_t)t * Q + c] = from_f32<TA>((row[c] * iq) * wq[c]);
+    if (!kc) return;
+    const int pos = token_pos[t];
+    const int page = block_table[(size_t)token_seq[t] * max_pages + pos / page_size];
+    if (page < 0) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    TA* dst = kc + ((size_t)page * page_size + pos % page_size) * R;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) dst[c] = from_f32<TA>((row[Q + c] * ik) * wkv[c]);
+}
+
+extern "C" int illm_latent_prep(const float* x, int ld, int Q, int R, const float* wq, const float* wkv, float eps, const int* token_pos,
+                                const int* token_seq, const int* block_table, int max_pages, int page_size, void* cq_out, void* kc,
+                                int act_dtype, int T, int* err, void* stream) {
+    if (T <= 0) return 0;
+    if (Q <= 0 || R <= 0 || !x || !cq_out || !wq || !wkv) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == ILLM_BF16)
+        illm_launch(latent_prep_kernel<bf16>, dim3(T), dim3(256), 0, s, x, ld, Q, R, wq, wkv, eps, token_pos, token_seq, block_table, max_pages,
+                    page_size, (bf16*)cq_out, (bf16*)kc, err);
+    else if (act_dtype == ILLM_F32)
+        illm_launch(latent_prep_kernel<float>, dim3(T), dim3(256), 0, s, x, ld, Q, R, wq, wkv, eps, token_pos, token_seq, block_table,
+                    max_pages, page_size, (float*)cq_out, (float*)kc, err);
+    else
+        return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}
+
+#define HG_BM 64
+#define HG_BN 64
+#define HG_BK 16
+
+// grid (ceil(N / 64), ceil(T / 64), heads); 256 threads, a 4 x 4 patch of outputs each
+template <typename TX, typename TW, typename TY, bool NN>
+__global__ void __launch_bounds__(256)
+head_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int T, int N, int K) {
+    pdl_grid_sync();
+    __shared__ float xs[HG_BK][HG_BM + 4];
+    __shared__ float ws[HG_BK][HG_BN + 4];
+    const int h = blockIdx.z, n0 = blockIdx.x * HG_BN, t0 = blockIdx.y * HG_BM;
+    const int H = gridDim.z;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HG_BK) {
+        for (int e = threadIdx.x; e < HG_BM * HG_BK; e += 256) {
+            const int m = e / HG_BK, k = e % HG_BK;
+            const int t = t0 + m;
+            xs[k][m] = (t < T && k0 + k < K) ? to_f32(x[((size_t)t * H + h) * K + k0 + k]) : 0.f;
+        }
+        for (int e = threadIdx.x; e < HG_BN * HG_BK; e += 256) {
+            int n, k;
+            if (NN) { n = e % HG_BN; k = e / HG_BN; } else { k = e % HG_BK; n = e / HG_BK; }
+            float v = 0.f;
+            if (n0 + n < N && k0 + k < K)
+                v = NN ? to_f32(w[((size_t)h * K + k0 + k) * N + n0 + n]) : to_f32(w[((size_t)h * N + n0 + n) * K + k0 + k]);
+            ws[k][n] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < HG_BK; k++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) y[((size_t)t * H + h) * N + n] = from_f32<TY>(acc[i][j]);
+        }
+    }
+}
+
+// x [T, heads * K] -> y [T, heads * N]; w [heads * N, K] (nn = 0) or [heads * K, N] (nn = 1).  dtype codes for x, w, y.
+extern "C" int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int T, int heads, int N, int K,
+                              int nn, void* stream) {
+    if (T <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || N <= 0 || K <= 0) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int t0 = 0; t0 < T; t0 += 65535 * HG_BM) {
+        const int n = min(T - t0, 65535 * HG_BM);
+        dim3 grid((N + HG_BN - 1) / HG_BN, (n + HG_BM - 1) / HG_BM, heads);
+        const size_t xo = (size_t)t0 * heads * K, yo = (size_t)t0 * heads * N;
+#define ILLM_HG(TX, TW, TY)                                                                                                             \
+    do {                                                                                                                                \
+        if (nn) illm_launch(head_gemm_kernel<TX, TW, TY, true>, grid, dim3(256), 0, s, (const TX*)x + xo, (const TW*)w, (TY*)y + yo, n, N, K); \
+        else illm_launch(head_gemm_kernel<TX, TW, TY, false>, grid, dim3(256), 0, s, (const TX*)x + xo, (const TW*)w, (TY*)y + yo, n, N, K); \
+    } while (0)
+        if (x_dtype == ILLM_F32 && w_dtype == ILLM_F32 && y_dtype == ILLM_F32) ILLM_HG(float, float, float);
+        else if (x_dtype == ILLM_F32 && w_dtype == ILLM_BF16 && y_dtype == ILLM_BF16) ILLM_HG(float, bf16, bf16);
+        else if (x_dtype == ILLM_BF16 && w_dtype == ILLM_BF16 && y_dtype == ILLM_BF16) ILLM_HG(bf16, bf16, bf16);
+        else if (x_dtype == ILLM_BF16 && w_dtype == ILLM_BF16 && y_dtype == ILLM_F32) ILLM_HG(bf16, bf16, float);
+        else return ILLM_ERR_BAD_ARG;
+#undef ILLM_HG
+    }
+    return illm_launch_status();
+}

@@ -1,0 +1,244 @@
+// Routed feed-forward (mixture of experts): every token goes through its `top` experts with the largest router
+// logits, weighted by the softmax over those logits alone.
+//
+//   moe_route_kernel   a warp per token: logits + bias (float32), `top` rounds of arg-max (the lowest index among
+//                      equal values), softmax over the chosen -> expert [T, top], weight [T, top]
+//   moe_layout_kernel  one block: rows per expert, their offsets, the (token, choice) pairs placed expert by expert
+//                      (row_of_pair, pair_of_row), and the list of row tiles (tile -> expert, first row, rows)
+//   moe_gemm_kernel    one block per (row tile, 64 output columns): rows of one expert against that expert's
+//                      matrix; GATED: hid = act(x W_gate^T) * (x W_up^T) with x gathered by token; else the down
+//                      product into float32 rows.  One chain of fused multiply-adds over the inner index per
+//                      output, so a row's bits depend neither on its place among the rows nor on the step.
+//   moe_combine_kernel out[t] = sum over the choices, in their order, of weight * row
+//
+// Which row a pair gets within its expert is decided by atomics in shared memory and may differ from run to run;
+// no result depends on it.
+#include "common.cuh"
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int top,
+                                 int* __restrict__ expert, float* __restrict__ weight) {
+    pdl_grid_sync();
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * E;
+    float best0 = 0.f, sum = 0.f;
+    for (int k = 0; k < top; k++) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            bool taken = false;
+            for (int j = 0; j < k; j++) taken |= expert[(size_t)t * top + j] == e;
+            if (taken) continue;
+            const float v = z[e] + (bias ? bias[e] : 0.f);
+            if (v > bv) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (k == 0) best0 = bv;
+        const float w = expf(bv - best0);
+        sum += w;
+        if (lane == 0) {
+            expert[(size_t)t * top + k] = bi;
+            weight[(size_t)t * top + k] = w;
+        }
+        __syncwarp();
+    }
+    if (lane < top) weight[(size_t)t * top + lane] /= sum;
+    for (int k = lane + 32; k < top; k += 32) weight[(size_t)t * top + k] /= sum;
+}
+
+// dynamic shared memory: 3 E + 1 ints
+__global__ void __launch_bounds__(1024)
+moe_layout_kernel(const int* __restrict__ expert, int P, int E, int bm, int* __restrict__ row_of_pair, int* __restrict__ pair_of_row,
+                  int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_rows, int max_tiles) {
+    pdl_grid_sync();
+    extern __shared__ int si[];
+    int* count = si;
+    int* offset = si + E;
+    int* cursor = si + 2 * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < P; i += blockDim.x) atomicAdd(&count[expert[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int rows = 0, tiles = 0;
+        for (int e = 0; e < E; e++) {
+            offset[e] = rows;
+            for (int r = 0; r < count[e]; r += bm, tiles++) {
+                tile_expert[tiles] = e;
+                tile_row0[tiles] = rows + r;
+                tile_rows[tiles] = min(bm, count[e] - r);
+            }
+            rows += count[e];
+        }
+        for (; tiles < max_tiles; tiles++) tile_rows[tiles] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < P; i += blockDim.x) {
+        const int e = expert[i];
+        const int row = offset[e] + atomicAdd(&cursor[e], 1);
+        row_of_pair[i] = row;
+        pair_of_row[row] = i;
+    }
+}
+
+__device__ __forceinline__ float moe_act(float v, int act) {
+    if (act == 1) return v / (1.0f + expf(-v));
+    if (act == 2) return fmaxf(v, 0.f);
+    if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+
+#define MOE_BN 64
+#define MOE_BK 16
+
+// grid (ceil(N / 64), max_tiles); 256 threads = 16 x 16, a (BM / 16) x 4 patch of outputs each.
+// GATED: x [T, K] gathered through pair_of_row / top, w [E, 2 N, K] (an expert's gate rows, then its up rows), y [P, N];
+// else x [P, K] by row, w [E, N, K], y [P, N].
+template <typename TX, typename TW, typename TY, int BM, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int N, int K, int top, int act,
+                const int* __restrict__ pair_of_row, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                const int* __restrict__ tile_rows) {
+    pdl_grid_sync();
+    constexpr int RM = BM / 16;
+    __shared__ float xs[MOE_BK][BM + 4];
+    __shared__ float ws[GATED ? 2 : 1][MOE_BK][MOE_BN + 4];
+    __shared__ int src_row[BM];
+    const int tile = blockIdx.y;
+    const int rows = tile_rows[tile];
+    if (rows == 0) return;
+    const int e = tile_expert[tile], row0 = tile_row0[tile], n0 = blockIdx.x * MOE_BN;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    for (int m = threadIdx.x; m < BM; m += 256) src_row[m] = m < rows ? (GATED ? pair_of_row[row0 + m] / top : row0 + m) : -1;
+    const TW* wg = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+    const TW* wu = wg + (size_t)N * K;
+    float acc[RM][4], acu[GATED ? RM : 1][4];
+#pragma unroll
+    for (int i = 0; i < RM; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            acc[i][j] = 0.f;
+            if (GATED) acu[i][j] = 0.f;
+        }
+    __syncthreads();
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+        for (int el = threadIdx.x; el < BM * MOE_BK; el += 256) {
+            const int m = el / MOE_BK, k = el % MOE_BK;
+            const int r = src_row[m];
+            xs[k][m] = (r >= 0 && k0 + k < K) ? to_f32(x[(size_t)r * K + k0 + k]) : 0.f;
+        }
+        for (int el = threadIdx.x; el < MOE_BN * MOE_BK; el += 256) {
+            const int n = el / MOE_BK, k = el % MOE_BK;
+            const bool in = n0 + n < N && k0 + k < K;
+            ws[0][k][n] = in ? to_f32(wg[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+            if (GATED) ws[1][k][n] = in ? to_f32(wu[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < MOE_BK; k++) {
+            float a[RM], b[4], c[4];
+#pragma unroll
+            for (int i = 0; i < RM; i++) a[i] = xs[k][ty * RM + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                b[j] = ws[0][k][tx * 4 + j];
+                if (GATED) c[j] = ws[GATED ? 1 : 0][k][tx * 4 + j];
+            }
+#pragma unroll
+            for (int i = 0; i < RM; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if (GATED) acu[i][j] = fmaf(a[i], c[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RM; i++) {
+        const int m = ty * RM + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            const float v = GATED ? moe_act(acc[i][j], act) * acu[i][j] : acc[i][j];
+            y[(size_t)(row0 + m) * N + n] = from_f32<TY>(v);
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
+                                   float* __restrict__ out, int D, int top, long long n) {
+    pdl_grid_sync();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / D;
+    const int c = (int)(i - t * D);
+    float acc = 0.f;
+    for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], rows[(size_t)row_of_pair[t * top + k] * D + c], acc);
+    out[i] = acc;
+}
+
+extern "C" int illm_moe_max_tiles(int T, int top, int E, int bm) { return (int)(((long long)T * top + bm - 1) / bm) + E; }
+extern "C" int illm_moe_row_tile(int T, int top) { return (long long)T * top <= 1024 ? 16 : 64; }
+
+// logits [T, E] float32 (without the bias); expert, weight [T, top]; row_of_pair, pair_of_row [T * top];
+// tile_* [illm_moe_max_tiles(T, top, E, illm_moe_row_tile(T, top))]
+extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int* expert, float* weight, int* row_of_pair,
+                              int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
+    const int bm = illm_moe_row_tile(T, top);
+    const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(moe_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        raised = true;
+    }
+    illm_launch(moe_layout_kernel, dim3(1), dim3(1024), smem, s, (const int*)expert, T * top, E, bm, row_of_pair, pair_of_row, tile_expert,
+                tile_row0, tile_rows, illm_moe_max_tiles(T, top, E, bm));
+    return illm_launch_status();
+}
+
+// gated != 0: x [T, K] (x_dtype), w [E, 2 N, K], y [T * top, N] in the dtype of x; else x [T * top, K], w [E, N, K], y float32
+extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
+                             int act, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                             void* stream) {
+    if (T <= 0) return 0;
+    if (N <= 0 || K <= 0 || x_dtype != w_dtype) return ILLM_ERR_BAD_ARG;
+    const int bm = illm_moe_row_tile(T, top);
+    const int tiles = illm_moe_max_tiles(T, top, E, bm);
+    if (tiles > 65535) return ILLM_ERR_BAD_ARG;
+    dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
+    cudaStream_t s = (cudaStream_t)stream;
+#define ILLM_MOE(TX, TY, BM, G)                                                                                                       \
+    illm_launch(moe_gemm_kernel<TX, TX, TY, BM, G>, grid, dim3(256), 0, s, (const TX*)x, (const TX*)w, (TY*)y, N, K, top, act, pair_of_row, \
+                tile_expert, tile_row0, tile_rows)
+    if (x_dtype == ILLM_BF16) {
+        if (gated) { if (bm == 16) ILLM_MOE(bf16, bf16, 16, true); else ILLM_MOE(bf16, bf16, 64, true); }
+        else { if (bm == 16) ILLM_MOE(bf16, float, 16, false); else ILLM_MOE(bf16, float, 64, false); }
+    } else if (x_dtype == ILLM_F32) {
+        if (gated) { if (bm == 16) ILLM_MOE(float, float, 16, true); else ILLM_MOE(float, float, 64, true); }
+        else { if (bm == 16) ILLM_MOE(float, float, 16, false); else ILLM_MOE(float, float, 64, false); }
+    } else {
+        return ILLM_ERR_BAD_ARG;
+    }
+#undef ILLM_MOE
+    return illm_launch_status();
+}
+
+extern "C" int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top,
+                                void* stream) {
+    if (T <= 0) return 0;
+    const long long n = (long long)T * D;
+    illm_launch(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, rows, row_of_pair, weight, out, D, top, n);
+    return illm_launch_status();
+}

@@ -458,10 +458,10 @@ Mat decay_scan(Device& dev, const Mat& x, const DecayScan& p, const StepView& ct
 }
 
 Mat group_norm_gate(Device& dev, const Mat& o, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
-                    DType out_dtype) {
+                    DType out_dtype, int w_len) {
     need(o, "the recurrence's output", true, DType::F32);
     Mat y = new_mat(dev, o.rows, o.cols, out_dtype);
-    check_kernel(illm_group_norm_gate((const float*)o.p, (int)o.rows, (int)o.cols, group, w, eps, gate, gate_ld, gate_act, y.p,
+    check_kernel(illm_group_norm_gate((const float*)o.p, (int)o.rows, (int)o.cols, group, w, w_len > 0 ? w_len : (int)o.cols, eps, gate, gate_ld, gate_act, y.p,
                                       code_of(out_dtype, "group_norm_gate"), dev.stream()),
                  "group_norm_gate");
     return y;
@@ -626,6 +626,149 @@ Mat attention(Device& dev, const Mat& qkv, const KVView& kv, const StepView& ctx
         return attention_prefill_tc(dev, qkv, kv, ctx, g, scale);
     if (!ctx.is_decode && attention_prefill_supported(qkv.dtype, nh, nkv, d)) return attention_prefill(dev, qkv, kv, ctx, g, scale);
     return attention_generic(dev, qkv, kv, ctx, g, scale);
+}
+
+// ---- pieces of further mixers, feed-forwards and embeddings
+
+int gate_act_from_name(const std::string& name) {
+    if (name == "silu") return kActSilu;
+    if (name == "relu") return kActRelu;
+    if (name == "gelu_tanh") return kActGeluTanh;
+    return -1;
+}
+
+Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act) {
+    if (act == kActSilu) return linear_gated(dev, backend, x, w);
+    Mat gu = linear(dev, backend, x, w, x.dtype, false).m;
+    if (gu.cols % 2) throw KernelError("gated activation: the packed projection must have an even number of columns");
+    Mat out = new_mat(dev, gu.rows, gu.cols / 2, gu.dtype);
+    check_kernel(illm_gated_act(gu.p, out.p, code_of(gu.dtype, "gated_act"), (int)gu.rows, (int)(gu.cols / 2), act, dev.stream()), "gated_act");
+    return out;
+}
+
+Mat take_columns(Device& dev, const Mat& x, long long off, long long n, DType dtype) {
+    need(x, "x", true, DType::F32);
+    if (off < 0 || n <= 0 || off + n > x.cols) throw KernelError("take_columns: the columns lie outside the matrix");
+    Mat y = new_mat(dev, x.rows, n, dtype);
+    check_kernel(illm_take_columns((const float*)x.p, (int)x.cols, (int)off, (int)n, y.p, code_of(dtype, "take_columns"), (int)x.rows, dev.stream()),
+                 "take_columns");
+    return y;
+}
+
+Mat join_rows(Device& dev, const Mat& a, const Mat& b, DType dtype) {
+    need(a, "a", true, DType::F32);
+    need(b, "b", true, DType::F32);
+    if (a.rows != b.rows || a.cols != b.cols) throw KernelError("join_rows: the two matrices differ in shape");
+    Mat y = new_mat(dev, a.rows, 2 * a.cols, dtype);
+    check_kernel(illm_join_rows((const float*)a.p, (const float*)b.p, (int)a.cols, y.p, code_of(dtype, "join_rows"), (int)a.rows, dev.stream()),
+                 "join_rows");
+    return y;
+}
+
+Mat bigram_embedding(Device& dev, const StepView& ctx, const Mat& table, const Mat& bigram, const BigramHash& hash, const StateView& last) {
+    need(table, "table");
+    need(bigram, "bigram table");
+    if (bigram.dtype != table.dtype || bigram.cols != table.cols || bigram.rows != hash.buckets + 1)
+        throw KernelError("bigram_embedding: the bigram table must have buckets + 1 rows of the embedding's width and dtype");
+    if (!last.state || last.dtype != DType::I32 || last.elements < 1) throw KernelError("bigram_embedding: the state entry must hold one int32 per sequence");
+    if (last.elements != 1) throw KernelError("bigram_embedding: the state entry must hold exactly one int32 per sequence");
+    Mat out = new_mat_exact(dev, ctx.T, table.cols, DType::F32);
+    check_kernel(illm_bigram_embedding(ctx.ids, ctx.token_pos, ctx.token_seq, ctx.cu_q, last.slots, (int*)last.state, table.p, bigram.p,
+                                       code_of(table.dtype, "bigram_embedding"), (float*)out.p, ctx.T, ctx.B, (int)table.cols, (int)table.rows,
+                                       (int)hash.buckets, hash.mul_prev, hash.mul_cur, ctx.err, dev.stream()),
+                 "bigram_embedding");
+    return out;
+}
+
+long long delta_rule_state_elements(int nh, int nkv, int d, int dv, int taps) {
+    return (long long)nh * d * dv + (long long)(taps - 1) * (2LL * nkv * d + (long long)nh * dv);
+}
+bool delta_rule_supported(int d, int dv, int taps) { return illm_delta_rule_supported(d, dv, taps) != 0; }
+
+Mat delta_rule(Device& dev, const Mat& x, const Mat& a, const DeltaRule& p, const StepView& ctx, const StateView& st) {
+    need(x, "the packed projection", true, DType::F32);
+    need(a, "the decay projection", true, DType::F32);
+    const long long T = x.rows, C = 2LL * p.n_kv_heads * p.head_dim + (long long)p.n_heads * p.v_head_dim;
+    if (a.rows != T || a.cols != (long long)p.n_heads * p.head_dim) throw KernelError("delta_rule: the decay projection must be [T, heads * head_dim]");
+    if (!st.state || st.dtype != DType::F32 || st.elements != delta_rule_state_elements(p.n_heads, p.n_kv_heads, p.head_dim, p.v_head_dim, p.taps))
+        throw KernelError("delta_rule: the state entry does not have this layer's size");
+    Mat qkv = new_mat_exact(dev, T, C, DType::F32), g = new_mat_exact(dev, T, a.cols, DType::F32), beta = new_mat_exact(dev, T, p.n_heads, DType::F32);
+    Mat out = new_mat_exact(dev, T, (long long)p.n_heads * p.v_head_dim, DType::F32);
+    check_kernel(illm_delta_rule((const float*)x.p, (int)T, (int)x.cols, p.q_off, p.k_off, p.v_off, p.b_off, (const float*)a.p, p.n_heads,
+                                 p.n_kv_heads, p.head_dim, p.v_head_dim, p.taps, p.conv_q, p.conv_k, p.conv_v, p.a_log, p.dt_bias, p.q_scale,
+                                 (float*)st.state, st.elements, st.slots, ctx.cu_q, ctx.token_pos, ctx.token_seq, ctx.seq_lens, (float*)qkv.p,
+                                 (float*)g.p, (float*)beta.p, (float*)out.p, ctx.B, dev.stream()),
+                 "delta_rule");
+    return out;
+}
+
+Mat latent_prep(Device& dev, const Mat& x, int q_rank, int kv_rank, const float* w_q, const float* w_kv, float eps, const StepView& ctx,
+                const KVView& kv, DType act_dtype) {
+    need(x, "the packed latent projection", true, DType::F32);
+    if (x.cols < q_rank + kv_rank) throw KernelError("latent_prep: the projection is narrower than the two latents");
+    if (kv.writes) {
+        if (!kv.k || kv.dtype != act_dtype || kv.n_kv_heads != 1 || kv.head_dim != kv_rank)
+            throw KernelError("latent_prep: the cache entry must hold one head of kv_rank channels in the activation dtype");
+    }
+    Mat cq = new_mat(dev, x.rows, q_rank, act_dtype);
+    check_kernel(illm_latent_prep((const float*)x.p, (int)x.cols, q_rank, kv_rank, w_q, w_kv, eps, ctx.token_pos, ctx.token_seq, kv.block_table,
+                                  kv.width, kv.page_size, cq.p, kv.writes ? kv.k : nullptr, code_of(act_dtype, "latent_prep"), (int)x.rows,
+                                  ctx.err, dev.stream()),
+                 "latent_prep");
+    return cq;
+}
+
+Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype) {
+    need(x, "x");
+    need(w, "w");
+    if (heads <= 0 || x.cols % heads) throw KernelError("head_linear: the input's width is not a multiple of the head count");
+    const long long K = x.cols / heads;
+    long long N;
+    if (transposed) {
+        if (w.rows != (long long)heads * K) throw KernelError("head_linear: the matrix must have heads * n_in rows");
+        N = w.cols;
+    } else {
+        if (w.cols != K || w.rows % heads) throw KernelError("head_linear: the matrix must be [heads * n_out, n_in]");
+        N = w.rows / heads;
+    }
+    Mat y = new_mat(dev, x.rows, (long long)heads * N, out_dtype);
+    const int rc = illm_head_gemm(x.p, code_of(x.dtype, "head_linear"), w.p, code_of(w.dtype, "head_linear"), y.p, code_of(out_dtype, "head_linear"),
+                                  (int)x.rows, heads, (int)N, (int)K, transposed ? 1 : 0, dev.stream());
+    if (rc == 10001) throw KernelError("head_linear: this combination of dtypes is not supported");
+    check_kernel(rc, "head_linear");
+    return y;
+}
+
+Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* router_bias, int E, int top, const Mat& w_gu, const Mat& w_down, int act) {
+    need(h, "h");
+    need(logits, "the router's logits", true, DType::F32);
+    const long long T = h.rows, D = h.cols;
+    if (logits.rows != T || logits.cols != E || top <= 0 || top > E) throw KernelError("moe: the router's logits must be [T, experts] and top within the experts");
+    if (w_gu.dtype != h.dtype || w_down.dtype != h.dtype || w_gu.cols != D || w_gu.rows % (2 * E) || w_down.cols * 2 * E != w_gu.rows ||
+        w_down.rows != (long long)E * D)
+        throw KernelError("moe: the experts' matrices do not match the input");
+    const long long F = w_down.cols, P = T * top;
+    const int tiles = illm_moe_max_tiles((int)T, top, E, illm_moe_row_tile((int)T, top));
+    int* expert = dev.alloc_n<int>((size_t)P);
+    float* weight = dev.alloc_n<float>((size_t)P);
+    int* row_of_pair = dev.alloc_n<int>((size_t)P);
+    int* pair_of_row = dev.alloc_n<int>((size_t)P);
+    int* tile_expert = dev.alloc_n<int>((size_t)tiles);
+    int* tile_row0 = dev.alloc_n<int>((size_t)tiles);
+    int* tile_rows = dev.alloc_n<int>((size_t)tiles);
+    check_kernel(illm_moe_route((const float*)logits.p, router_bias, (int)T, E, top, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0,
+                                tile_rows, dev.stream()),
+                 "moe_route");
+    const int code = code_of(h.dtype, "moe");
+    Mat hid = new_mat_exact(dev, P, F, h.dtype), rows = new_mat_exact(dev, P, D, DType::F32), out = new_mat_exact(dev, T, D, DType::F32);
+    check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)F, (int)D, 1, act, pair_of_row, tile_expert, tile_row0, tile_rows,
+                               dev.stream()),
+                 "moe_gemm (gate/up)");
+    check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, pair_of_row, tile_expert, tile_row0, tile_rows,
+                               dev.stream()),
+                 "moe_gemm (down)");
+    check_kernel(illm_moe_combine((const float*)rows.p, row_of_pair, weight, (float*)out.p, (int)T, (int)D, top, dev.stream()), "moe_combine");
+    return out;
 }
 
 // ---- sampling and utilities

@@ -215,9 +215,53 @@ struct DecayScan {
 int decay_scan_segments(int B, int n_heads, int v_head_dim, int max_q, int n_sms);
 Mat decay_scan(Device& dev, const Mat& x_f32, const DecayScan& p, const StepView& ctx, const StateView& st);
 bool decay_scan_supported(int head_dim, int v_head_dim);
-// y = o / sqrt(mean over groups of `group` columns (o^2) + eps) (* w) * act(gate), gate_act 1: silu, 2: sigmoid
+// y = o / sqrt(mean over groups of `group` columns (o^2) + eps) (* w) * act(gate), gate_act 1: silu, 2: sigmoid;
+// w has w_len entries (0: the whole row), a shorter one repeats along the row (one group's weight for every group)
 Mat group_norm_gate(Device& dev, const Mat& o_f32, int group, const float* w, float eps, const float* gate, int gate_ld, int gate_act,
-                    DType out_dtype);
+                    DType out_dtype, int w_len = 0);
+
+// ---- pieces of further mixers, feed-forwards and embeddings
+
+// Activations of the gated feed-forward: act(gate) * up.
+enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3 };
+int gate_act_from_name(const std::string& name);        // ConfigError-free: -1 for an unknown name
+// act(gate) * up of x . w^T for any GateAct (silu takes the fused kernels of linear_gated)
+Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act);
+// columns [off, off + n) of a float32 matrix as a contiguous matrix of `dtype`
+Mat take_columns(Device& dev, const Mat& x_f32, long long off, long long n, DType dtype);
+// [a, b] row by row (two float32 matrices of equal shape) as a matrix of `dtype`
+Mat join_rows(Device& dev, const Mat& a_f32, const Mat& b_f32, DType dtype);
+
+// Token embedding plus a hashed bigram table (csrc/bigram_embedding.cu); last_token: the int32 per-sequence state.
+struct BigramHash { long long buckets = 0, mul_prev = 0, mul_cur = 0; };
+Mat bigram_embedding(Device& dev, const StepView& ctx, const Mat& table, const Mat& bigram, const BigramHash& hash, const StateView& last_token);
+
+// The gated delta rule with a decay per head and key channel (csrc/delta_state.cu).  x_f32: the packed float32
+// projection with q, k, v and beta's logits at the given columns; a_f32 [T, heads * head_dim]: the decay
+// projection.  The state entry holds S and the convolution's rows (delta_rule_state_elements).  Returns float32
+// [T, heads * v_head_dim].
+struct DeltaRule {
+    int q_off = 0, k_off = 0, v_off = 0, b_off = 0;
+    int n_heads = 0, n_kv_heads = 0, head_dim = 0, v_head_dim = 0, taps = 1;
+    const float *conv_q = nullptr, *conv_k = nullptr, *conv_v = nullptr;     // float32 [channels, taps]
+    const float *a_log = nullptr, *dt_bias = nullptr;                        // float32 [heads], [heads * head_dim]
+    float q_scale = 1.f;
+};
+long long delta_rule_state_elements(int n_heads, int n_kv_heads, int head_dim, int v_head_dim, int taps);
+bool delta_rule_supported(int head_dim, int v_head_dim, int taps);
+Mat delta_rule(Device& dev, const Mat& x_f32, const Mat& a_f32, const DeltaRule& p, const StepView& ctx, const StateView& st);
+
+// Attention through latents (csrc/latent_attention.cu): the two norms and the cache write; returns the normed
+// query latent [T, q_rank] in `act_dtype`.  kv: a keys-only entry of one head of kv_rank channels.
+Mat latent_prep(Device& dev, const Mat& x_f32, int q_rank, int kv_rank, const float* w_q, const float* w_kv, float eps, const StepView& ctx,
+                const KVView& kv, DType act_dtype);
+// y[t, h, :] = W_h x[t, h, :] (transposed = false, w [heads * n_out, n_in]) or W_h^T x[t, h, :] (w [heads * n_in, n_out])
+Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype);
+
+// Routed feed-forward (csrc/moe.cu).  logits float32 [T, experts] without the bias.  w_gate_up [experts * 2 ff, hidden]
+// (per expert its gate rows, then its up rows), w_down [experts * hidden, ff].  Returns float32 [T, hidden].
+Mat moe_forward(Device& dev, const Mat& h, const Mat& logits_f32, const float* router_bias, int experts, int top, const Mat& w_gate_up,
+                const Mat& w_down, int act);
 
 // float32 [B, V] -> int32 [B], the lowest id among equal maxima.
 int* argmax(Device& dev, const float* logits, long long B, long long V, int* out /* nullptr: from the arena */);

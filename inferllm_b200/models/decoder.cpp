@@ -32,6 +32,7 @@ DecoderModel::DecoderModel(const ModelSpec& s, Runtime* runtime) : spec(s), rt(r
     }
     final_norm_ = build_norm(spec.final_norm, rt);
     head_ = build_head(spec.head, rt);
+    if (!spec.reentry.kind.empty()) reentry_ = build_feed_forward(spec.reentry, rt);
 }
 
 std::vector<std::pair<std::string, Part*>> DecoderModel::owners() const {
@@ -43,6 +44,7 @@ std::vector<std::pair<std::string, Part*>> DecoderModel::owners() const {
         if (layers_[i].ffn) out.emplace_back(ls.prefix + role_name(ls, "ffn"), layers_[i].ffn.get());
         for (auto& n : layers_[i].norms) out.emplace_back(ls.prefix + role_name(ls, n.first), n.second.get());
     }
+    if (reentry_) out.emplace_back(spec.reentry.get_string("name", ""), reentry_.get());
     out.emplace_back(spec.final_norm.get_string("name", ""), final_norm_.get());
     out.emplace_back(spec.head.get_string("name", ""), head_.get());
     return out;
@@ -69,17 +71,42 @@ std::map<int, CacheRequest> DecoderModel::cache_requests() const {
     std::map<int, CacheRequest> out;
     for (const ScheduleEntry& e : spec.schedule)
         if (e.writes) out[e.cache] = layers_[(size_t)e.layer].mixer->cache_request();
+    const CacheRequest er = embedding_->cache_request();
+    if (er.kind != CacheRequest::None) out[kEmbeddingCacheEntry] = er;
     return out;
 }
 
 Mat DecoderModel::forward(const StepContext& ctx, const SequenceCache& cache, const std::vector<const int*>& tables_dev) {
     Device& dev = *rt->dev;
-    ResidualStream stream = embedding_->forward(ctx);
+    ResidualStream stream;
+    if (cache.kind_of(kEmbeddingCacheEntry) == SequenceCache::State) {
+        CacheView ev;
+        ev.kind = CacheView::State;
+        ev.st = cache.state_view(kEmbeddingCacheEntry, ctx.slots);
+        stream = embedding_->forward_with_state(ctx, ev);
+    } else {
+        stream = embedding_->forward(ctx);
+    }
+    Mat x0;      // the embedding output, kept for the entries that re-enter the stream
+    if (reentry_) {
+        stream.flush();
+        x0 = stream.x;
+        x0.p = dev.alloc(x0.bytes());
+        check_cuda(cudaMemcpyAsync(x0.p, stream.x.p, x0.bytes(), cudaMemcpyDeviceToDevice, dev.stream()), "keeping the embedding output");
+    }
     int turn = 0;
     for (const ScheduleEntry& e : spec.schedule) {
         // the layers' activations take turns in two lanes of the step arena: what a layer leaves for the
         // next one (its last output, pending in the stream) is read before this lane's turn comes again
         dev.set_lane(1 + (turn++ & 1), true);
+        if (e.reenter) {
+            // x <- W [x; x0]; the result goes back into the stream's own rows, which outlive the lanes
+            stream.flush();
+            MatOrPartials y = reentry_->forward(ops::join_rows(dev, stream.x, x0, rt->dtype), ctx, false);
+            if (y.m.dtype != DType::F32 || y.m.rows != stream.x.rows || y.m.cols != stream.x.cols)
+                throw EngineError("the re-entry map must give float32 rows of the stream's width");
+            check_cuda(cudaMemcpyAsync(stream.x.p, y.m.p, stream.x.bytes(), cudaMemcpyDeviceToDevice, dev.stream()), "re-entering the stream");
+        }
         CacheView view;
         switch (cache.kind_of(e.cache)) {
             case SequenceCache::KV:
@@ -112,7 +139,7 @@ bool DecoderModel::graph_safe() const {
     return true;
 }
 bool DecoderModel::pad_safe() const {
-    if (!graph_safe()) return false;
+    if (!graph_safe() || !embedding_->pad_safe()) return false;
     for (const Layer& l : layers_)
         if (!l.mixer->pad_safe()) return false;
     return true;

@@ -18,6 +18,9 @@ namespace illm {
 
 class SequenceCache;
 
+// The cache entry number of an embedding that keeps per-sequence state (schedule entries count from 0).
+constexpr int kEmbeddingCacheEntry = -1;
+
 class DecoderModel {
 public:
     // runtime == nullptr: the parts only declare their tensors (for checking a folder or writing a
@@ -52,6 +55,7 @@ private:
     };
     std::vector<std::pair<std::string, Part*>> owners() const;
     std::unique_ptr<EmbeddingPart> embedding_;
+    std::unique_ptr<FeedForward> reentry_;      // the map of [stream; embedding output] before the entries marked `reenter`
     std::vector<Layer> layers_;
     std::unique_ptr<Norm> final_norm_;
     std::unique_ptr<HeadPart> head_;

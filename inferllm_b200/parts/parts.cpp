@@ -5,6 +5,9 @@
 namespace illm {
 
 void register_decay_parts(std::map<std::string, PartFactory<Mixer>>& mixers);      // parts/decay_mixer.cpp
+void register_delta_parts(std::map<std::string, PartFactory<Mixer>>& mixers);      // parts/delta_mixer.cpp
+void register_latent_parts(std::map<std::string, PartFactory<Mixer>>& mixers);     // parts/latent_mixer.cpp
+void register_routed_parts(std::map<std::string, PartFactory<FeedForward>>& ffs);  // parts/routed_mlp.cpp
 
 // ---- registries
 
@@ -509,18 +512,20 @@ struct Attention : Mixer {
 // into one [2I, H] matrix at load, row 2i the gate row and row 2i + 1 the up row of output i, so that
 // one product feeds the activation, and where the package's own kernels run that product the
 // activation is their epilogue (ops::linear_gated).
-// `names` renames the three tensors; `output_dtype` = "float32" leaves the down projection unrounded.
+// `names` renames the three tensors; `output_dtype` = "float32" leaves the down projection unrounded;
+// `activation` is "silu" (default), "relu" or "gelu_tanh" (the latter two run the product and a kernel of their own).
 struct GatedMLP : FeedForward {
     long long hidden, inter;
     bool out_f32;
+    int act;
     std::string n_gate = "gate_proj.weight", n_up = "up_proj.weight", n_down = "down_proj.weight";
     DeviceBuffer gu_buf, down_buf;
     Mat w_gate_up, w_down;
     GatedMLP(const PartSpec& s, Runtime* rt)
             : FeedForward(s, rt), hidden(s.get_int("hidden_size")), inter(s.get_int("intermediate_size")),
               out_f32(s.get_string("output_dtype", "compute") == "float32") {
-        const std::string act = s.get_string("activation", "silu");
-        if (act != "silu") throw ConfigError("gated_mlp: activation '" + act + "' is not supported (only 'silu')");
+        act = ops::gate_act_from_name(s.get_string("activation", "silu"));
+        if (act < 0) throw ConfigError("gated_mlp: activation '" + s.get_string("activation", "silu") + "' is not supported (silu, relu, gelu_tanh)");
         if (hidden <= 0 || inter <= 0) throw ConfigError("gated_mlp: sizes must be positive");
         if (s.has("names")) {
             const Json& n = s.params.at("names");
@@ -544,7 +549,7 @@ struct GatedMLP : FeedForward {
     }
     MatOrPartials forward(const Mat& h, const StepContext&, bool may_defer) override {
         Device& dev = *rt->dev;
-        return ops::linear(dev, rt->gemm, ops::linear_gated(dev, rt->gemm, h, w_gate_up), w_down, out_f32 ? DType::F32 : rt->dtype,
+        return ops::linear(dev, rt->gemm, ops::linear_gated_act(dev, rt->gemm, h, w_gate_up, act), w_down, out_f32 ? DType::F32 : rt->dtype,
                            may_defer);
     }
 };
@@ -563,6 +568,62 @@ struct Embedding : EmbeddingPart {
         ResidualStream s;
         s.dev = rt->dev;
         s.x = ops::embedding(*rt->dev, ctx.ids, ctx.T, weight.m, ctx.err);
+        return s;
+    }
+    const Mat* table() const override { return &weight.m; }
+};
+
+// A plain linear map y = W x without bias, as a feed-forward part: "linear" with `in_size`, `out_size`, the tensor's
+// name `tensor` and `output_dtype`.  A model's re-entry map (ModelSpec::reentry) is one.
+struct LinearMap : FeedForward {
+    long long n_in, n_out;
+    bool out_f32;
+    std::string tensor;
+    OwnedMat w;
+    LinearMap(const PartSpec& s, Runtime* rt)
+            : FeedForward(s, rt), n_in(s.get_int("in_size")), n_out(s.get_int("out_size")),
+              out_f32(s.get_string("output_dtype", "compute") == "float32"), tensor(s.get_string("tensor", "weight")) {
+        if (n_in <= 0 || n_out <= 0) throw ConfigError("linear: sizes must be positive");
+    }
+    TensorDecls tensors() const override { return {{tensor, TensorDecl{{n_out, n_in}}}}; }
+    void load(TensorSource& src) override { w = fetch_owned(rt, src, tensor, rt->dtype, "a linear map's matrix"); }
+    MatOrPartials forward(const Mat& h, const StepContext&, bool may_defer) override {
+        return ops::linear(*rt->dev, rt->gemm, h, w.m, out_f32 ? DType::F32 : rt->dtype, may_defer);
+    }
+};
+
+// Token embedding plus a hashed bigram table: x[t] = W[id_t] + G[(id_{t-1} * mul_prev + id_t * mul_cur) mod buckets],
+// and G's last row (number `buckets`) for a sequence's first token.  The previous token of a step's first token is
+// per-sequence state: one int32 per slot in a cache entry of the embedding's own.
+struct BigramEmbedding : EmbeddingPart {
+    long long vocab, hidden;
+    ops::BigramHash hash;
+    std::string tensor, bigram_tensor;
+    OwnedMat weight, bigram;
+    BigramEmbedding(const PartSpec& s, Runtime* rt)
+            : EmbeddingPart(s, rt), vocab(s.get_int("vocab_size")), hidden(s.get_int("hidden_size")), tensor(s.get_string("tensor", "weight")),
+              bigram_tensor(s.get_string("bigram_tensor", "bigram.weight")) {
+        hash.buckets = s.get_int("buckets");
+        hash.mul_prev = s.get_int("mul_prev");
+        hash.mul_cur = s.get_int("mul_cur");
+        if (hash.buckets <= 0 || hash.buckets >= (1LL << 31) || hash.mul_prev < 0 || hash.mul_cur < 0)
+            throw ConfigError("bigram_embedding: buckets must be positive and the multipliers not negative");
+    }
+    TensorDecls tensors() const override {
+        return {{tensor, TensorDecl{{vocab, hidden}}}, {bigram_tensor, TensorDecl{{hash.buckets + 1, hidden}}}};
+    }
+    void load(TensorSource& src) override {
+        weight = fetch_owned(rt, src, tensor, rt->dtype, "the embedding table");
+        bigram = fetch_owned(rt, src, bigram_tensor, rt->dtype, "the bigram table");
+    }
+    CacheRequest cache_request() const override { return CacheRequest::state({1}, DType::I32); }
+    bool pad_safe() const override { return false; }
+    ResidualStream forward(const StepContext&) override { throw EngineError("bigram_embedding: needs its per-sequence state"); }
+    ResidualStream forward_with_state(const StepContext& ctx, const CacheView& cache) override {
+        if (cache.kind != CacheView::State) throw EngineError("bigram_embedding: the embedding's cache entry holds no state");
+        ResidualStream s;
+        s.dev = rt->dev;
+        s.x = ops::bigram_embedding(*rt->dev, ctx, weight.m, bigram.m, hash, cache.st);
         return s;
     }
     const Mat* table() const override { return &weight.m; }
@@ -637,8 +698,28 @@ struct PostNormBlock : Block {
     }
 };
 
+// "parallel": one norm, and both sublayers read its output:
+//     h = norm1(x);  x = x + mixer(h) + ffn(h)
+// (a layer without a feed-forward adds the mixer alone).  The sublayers' outputs are added to the float32 stream one
+// after the other, unrounded if they come in float32.
+struct ParallelBlock : Block {
+    void forward(ResidualStream& stream, const StepContext& ctx, const CacheView& cache, bool writes) override {
+        stream.flush();
+        Mat h = norms.at("norm1")->forward(stream, nullptr, 0);
+        stream.add(mixer->forward(h, ctx, cache, writes, false));
+        if (ffn) stream.add(ffn->forward(h, ctx, false));
+        stream.flush();
+    }
+};
+
 void register_builtin_parts() {
     register_decay_parts(reg<Mixer>());
+    register_delta_parts(reg<Mixer>());
+    register_latent_parts(reg<Mixer>());
+    register_routed_parts(reg<FeedForward>());
+    block_reg()["parallel"] = BlockKind{{"norm1"}, [] { return std::unique_ptr<Block>(new ParallelBlock); }};
+    reg<FeedForward>()["linear"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<FeedForward>(new LinearMap(s, rt)); };
+    reg<EmbeddingPart>()["bigram_embedding"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<EmbeddingPart>(new BigramEmbedding(s, rt)); };
     block_reg()["postnorm"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
     block_reg()["postnorm_mixer"] = BlockKind{{"norm1", "norm2"}, [] { return std::unique_ptr<Block>(new PostNormBlock); }};
     reg<Norm>()["rmsnorm"] = [](const PartSpec& s, Runtime* rt) { return std::unique_ptr<Norm>(new RMSNorm(s, rt)); };

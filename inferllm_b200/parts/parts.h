@@ -45,7 +45,7 @@ struct Runtime {
 // A tensor that a part needs.  init: "matrix" -> N(0, 0.02); "norm" -> 1 + N(0, 0.02); "int" -> an
 // integer table (kept int32).  Used by the loader to check shapes and by the random-weights writer.
 struct TensorDecl {
-    std::vector<long long> shape;
+    std::vector<long long> shape;      // a size of -1 is whatever the weight file has (the part reads it at load)
     std::string init = "matrix";
     // true: a weight file may leave the tensor out (the part then does without it); random models have none
     bool optional = false;
@@ -218,6 +218,12 @@ public:
     using Part::Part;
     virtual ResidualStream forward(const StepContext& ctx) = 0;     // ctx.ids -> the float32 stream [T, H]
     virtual const Mat* table() const { return nullptr; }            // what a tied head may use
+    // An embedding that depends on earlier tokens of the sequence keeps per-sequence state: it asks for a cache
+    // entry of its own here and is then run through forward_with_state.
+    virtual CacheRequest cache_request() const { return CacheRequest(); }
+    virtual ResidualStream forward_with_state(const StepContext& ctx, const CacheView&) { return forward(ctx); }
+    // false if tokens appended behind a sequence's real ones would change what is kept (see Mixer::pad_safe)
+    virtual bool pad_safe() const { return true; }
 };
 
 class HeadPart : public Part {

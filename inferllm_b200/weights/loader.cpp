@@ -30,7 +30,13 @@ void check_names_and_shapes(const std::vector<std::pair<std::string, TensorDecl>
         if (!by_name.count(r.first) && !ends_with(r.first, "rotary_emb.inv_freq")) unexpected.push_back(r.first);
     for (auto& d : by_name) {
         auto it = records.find(d.first);
-        if (it != records.end() && it->second.shape != d.second->shape)
+        auto fits = [](const std::vector<long long>& have, const std::vector<long long>& want) {
+            if (have.size() != want.size()) return false;
+            for (size_t i = 0; i < have.size(); i++)
+                if (want[i] >= 0 && want[i] != have[i]) return false;
+            return true;
+        };
+        if (it != records.end() && !fits(it->second.shape, d.second->shape))
             wrong.push_back(d.first + " expected " + shape_str(d.second->shape) + " found " + shape_str(it->second.shape));
     }
     if (missing.empty() && unexpected.empty() && wrong.empty()) return;
