@@ -176,6 +176,27 @@ def vokelix_config(z, vocab=32000, max_positions=4096):
                 max_positions=max_positions)
 
 
+VIZOSUN_LAYERS = (("channel_delta", "dense"), ("latent_attention", "moe"), ("channel_delta", "moe"), ("latent_attention", "dense"),
+                  ("channel_delta", "dense"), ("latent_attention", "moe"))
+
+
+def vizosun_config(z, vocab=32000, max_positions=4096):
+    """Six layers of the Vizosun design at the size z: delta-rule layers with the linear layers' head count and head
+    size, latent attention with a latent of 128 channels and a window of 1,024, dense feed-forwards of the size's
+    width, routed ones with 8 experts of half that width of which a token uses 2 (the same active matrix elements),
+    layers 1 and 2 run twice (so eight layer runs), the bigram table."""
+    layers = []
+    for t, kind in VIZOSUN_LAYERS:
+        if t == "channel_delta":
+            m = dict(heads=z["lin_heads"], kv_heads=max(1, z["lin_heads"] // 2), dim=z["lin_d"], vdim=z["lin_d"], conv=4, a_rank=64, g_rank=64)
+        else:
+            m = dict(heads=z["heads"], dim=z["d"], vdim=z["d"], q_rank=z["width"] // 4, kv_rank=128, scale=z["d"] ** -0.5, mask=dict(size=1024))
+        mlp = dict(kind="dense", ff=z["ff"]) if kind == "dense" else dict(kind="moe", expert=dict(ff=z["ff"] // 2), router=dict(experts=8, top=2))
+        layers.append(dict(type=t, mixer=m, mlp=mlp))
+    return dict(architecture="Vizosun", layers=layers, norm=dict(eps=1e-5), vocab=vocab, width=z["width"], max_positions=max_positions,
+                embedding=dict(bigram=dict(buckets=65521, mul_prev=1000003, mul_cur=31)), loop=dict(start=1, stop=3, times=2))
+
+
 def llama_twin(z, vocab=32000, max_positions=4096):
     return dict(architectures=["LlamaForCausalLM"], hidden_size=z["width"], num_hidden_layers=len(DESIGN_LAYERS),
                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["d"], intermediate_size=z["ff"],
@@ -184,8 +205,9 @@ def llama_twin(z, vocab=32000, max_positions=4096):
 
 
 def run_design(args):
-    """Prompt and decode throughput of the Vokelix design at a few layer sizes, each beside a LLaMA
-    model of the same width, feed-forward, head counts and number of layers, through Engine.step; and
+    """Prompt and decode throughput of a design at a few layer sizes, each beside the closest other
+    model of the same width, feed-forward, head counts and number of layers (Vokelix beside LLaMA;
+    Vizosun beside Vokelix and LLaMA), through Engine.step; and
     where each of the two spends its time, kernel by kernel (the driver's activity records of one step).
     One JSON line per (size, model)."""
     import torch
@@ -221,7 +243,10 @@ def run_design(args):
 
     for size in args.design_size.split(","):
         z = DESIGN_SIZES[size]
-        for which, cfgd in (("vokelix", vokelix_config(z)), ("llama", llama_twin(z))):
+        arms = (("vokelix", vokelix_config(z)), ("llama", llama_twin(z)))
+        if args.design == "vizosun":
+            arms = (("vizosun", vizosun_config(z)),) + arms
+        for which, cfgd in arms:
             eng = Engine.from_config(config_from_dict(cfgd), EngineOptions(dtype="bfloat16", max_tokens=max(B * (C + 64), NP * (T + 64)) + 64,
                                                                            max_seq_len=4096, max_batch=max(B, NP, 8)), seed=0)
             ids = torch.randint(0, 32000, (T,), generator=g).tolist()
@@ -250,7 +275,7 @@ def run_design(args):
             dec_ms = timed(one, K)
             for s in slots:
                 eng.end_sequence(s)
-            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else len(DESIGN_LAYERS),
+            print(json.dumps({"design": which, "size": size, "layers": list(DESIGN_LAYERS) if which == "vokelix" else ["/".join(x) for x in VIZOSUN_LAYERS] if which == "vizosun" else len(DESIGN_LAYERS),
                               "prefill_tokens": T, "prefill_prompts": NP, "prefill_ms": round(pf_ms, 3), "prefill_tok_s": round(NP * T / pf_ms * 1e3, 1),
                               "decode_batch": B, "decode_context": C, "decode_ms": round(dec_ms, 4),
                               "decode_tok_s": round(B / dec_ms * 1e3, 1), "prefill_kernels_us": pf_kernels,
@@ -483,7 +508,7 @@ def main():
                     "lengths uniform in [MIN, MAX] (seeded) prefilled in one step of unequal lengths, then NEW tokens "
                     "each (or 'toN': until position N), through the Python entry point; 'config' = the workload of --model "
                     "(8b: 16:64:2048:256, 13b: 32:128:1024:to4096)")
-    ap.add_argument("--design", choices=["vokelix"], help="beside the default workload: prompt and decode throughput of this design "
+    ap.add_argument("--design", choices=["vokelix", "vizosun"], help="beside the default workload: prompt and decode throughput of this design "
                     "at a few layer sizes, each next to LLaMA layers of equal size, with the time per kernel")
     ap.add_argument("--design-size", default="1k,2k,4k", help="with --design: sizes to run (1k, 2k, 4k: the width)")
     ap.add_argument("--design-tokens", type=int, default=2048, help="with --design: tokens of the prompt")

@@ -52,9 +52,9 @@ int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void*
 
 // moe.cu
 int illm_moe_max_tiles(int T, int top, int E, int bm);
-int illm_moe_row_tile(int T, int top);
-int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
-int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
+int illm_moe_row_tile(int T, int top, int tensor_cores);
+int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
+int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
 int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top, void* stream);
 
 // stream_ops.cu

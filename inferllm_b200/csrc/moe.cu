@@ -173,6 +173,131 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
     }
 }
 
+
+// ---- the same product on tensor cores (bfloat16, K a multiple of 8)
+//
+// A 64 x 128 tile per block, 8 warps of 32 x 32, K in slabs of 32 through a ring of three shared-memory stages filled
+// by cp.async (rows padded to 80 bytes, so that ldmatrix reads without bank conflicts); rows of the tile beyond the
+// expert's rows and columns beyond N are zero-filled on the way in and masked on the way out.  GATED keeps two
+// accumulators (gate and up) and stores act(gate) * up.
+#define MM_BM 64
+#define MM_BN 128
+#define MM_BK 32
+#define MM_LD 40            // bf16 elements per padded row
+#define MM_STAGES 3
+
+__device__ __forceinline__ unsigned mm_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mm_cp16(unsigned dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void mm_ldsm4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mm_mma(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TY, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int N, int K, int top, int act,
+                    const int* __restrict__ pair_of_row, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                    const int* __restrict__ tile_rows) {
+    pdl_grid_sync();
+    extern __shared__ __align__(16) unsigned char mm_raw[];
+    constexpr int NB = GATED ? 2 : 1;
+    constexpr int A_ELEMS = MM_BM * MM_LD, B_ELEMS = MM_BN * MM_LD, STAGE_ELEMS = A_ELEMS + NB * B_ELEMS;
+    bf16* sm = reinterpret_cast<bf16*>(mm_raw);
+    __shared__ int src_row[MM_BM];
+    const int tile = blockIdx.y;
+    const int rows = tile_rows[tile];
+    if (rows == 0) return;
+    const int e = tile_expert[tile], row0 = tile_row0[tile], n0 = blockIdx.x * MM_BN;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 2, wn = warp & 3;
+    for (int m = tid; m < MM_BM; m += 256) src_row[m] = m < rows ? (GATED ? pair_of_row[row0 + m] / top : row0 + m) : -1;
+    __syncthreads();
+    const bf16* wg = w + (size_t)e * NB * N * K;
+    const int KT = (K + MM_BK - 1) / MM_BK;
+    // what this thread copies per slab: one 16-byte piece of A, two of each B
+    const int a_r = tid >> 2, a_c = (tid & 3) * 8;
+    const int a_src = src_row[a_r];
+    auto load = [&](int stage, int kt) {
+        bf16* base = sm + (size_t)stage * STAGE_ELEMS;
+        const int k = kt * MM_BK + a_c;
+        {
+            const bool ok = a_src >= 0 && k < K;
+            mm_cp16(mm_smem(base + a_r * MM_LD + a_c), ok ? (const void*)(x + (size_t)a_src * K + k) : (const void*)x, ok ? 16 : 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int r = a_r + i * 64, n = n0 + r;
+            const bool ok = n < N && k < K;
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+                mm_cp16(mm_smem(base + A_ELEMS + b * B_ELEMS + r * MM_LD + a_c), ok ? (const void*)(wg + ((size_t)b * N + n) * K + k) : (const void*)w,
+                        ok ? 16 : 0);
+        }
+    };
+    float acc[NB][2][4][4];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) acc[b][i][j][c] = 0.f;
+    for (int s = 0; s < MM_STAGES - 1; s++) {
+        if (s < KT) load(s, s);
+        asm volatile("cp.async.commit_group;\n" ::);
+    }
+    const bool busy = wm * 32 < rows;      // a warp whose 32 rows lie beyond the expert's rows only helps to copy
+    for (int kt = 0; kt < KT; kt++) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(MM_STAGES - 2));
+        __syncthreads();
+        if (kt + MM_STAGES - 1 < KT) load((kt + MM_STAGES - 1) % MM_STAGES, kt + MM_STAGES - 1);
+        asm volatile("cp.async.commit_group;\n" ::);
+        if (!busy) continue;
+        const bf16* base = sm + (size_t)(kt % MM_STAGES) * STAGE_ELEMS;
+#pragma unroll
+        for (int ks = 0; ks < MM_BK; ks += 16) {
+            unsigned a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+                mm_ldsm4(a[i][0], a[i][1], a[i][2], a[i][3], mm_smem(base + (wm * 32 + i * 16 + (lane & 15)) * MM_LD + ks + (lane >> 4) * 8));
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                const bf16* bb = base + A_ELEMS + b * B_ELEMS;
+#pragma unroll
+                for (int jj = 0; jj < 2; jj++) {
+                    unsigned r0, r1, r2, r3;
+                    mm_ldsm4(r0, r1, r2, r3, mm_smem(bb + (wn * 32 + jj * 16 + (lane & 7) + ((lane >> 4) << 3)) * MM_LD + ks + ((lane >> 3) & 1) * 8));
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        mm_mma(acc[b][i][jj * 2], a[i], r0, r1);
+                        mm_mma(acc[b][i][jj * 2 + 1], a[i], r2, r3);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    if (!busy) return;
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int m = wm * 32 + i * 16 + (lane >> 2) + (c >> 1) * 8;
+                const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + (c & 1);
+                if (m >= rows || n >= N) continue;
+                const float v = GATED ? moe_act(acc[0][i][j][c], act) * acc[NB - 1][i][j][c] : acc[0][i][j][c];
+                y[(size_t)(row0 + m) * N + n] = from_f32<TY>(v);
+            }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
                                    float* __restrict__ out, int D, int top, long long n) {
     pdl_grid_sync();
@@ -186,17 +311,17 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
 }
 
 extern "C" int illm_moe_max_tiles(int T, int top, int E, int bm) { return (int)(((long long)T * top + bm - 1) / bm) + E; }
-extern "C" int illm_moe_row_tile(int T, int top) { return (long long)T * top <= 1024 ? 16 : 64; }
+// rows per tile: the tensor-core kernel takes 64; the plain one 16 for steps of few tokens, else 64
+extern "C" int illm_moe_row_tile(int T, int top, int tensor_cores) { return tensor_cores || (long long)T * top > 1024 ? 64 : 16; }
 
 // logits [T, E] float32 (without the bias); expert, weight [T, top]; row_of_pair, pair_of_row [T * top];
-// tile_* [illm_moe_max_tiles(T, top, E, illm_moe_row_tile(T, top))]
-extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int* expert, float* weight, int* row_of_pair,
+// tile_* [illm_moe_max_tiles(T, top, E, bm)], bm = illm_moe_row_tile(..)
+extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair,
                               int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || top > E || (bm != 16 && bm != 64) || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
-    const int bm = illm_moe_row_tile(T, top);
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     static bool raised = false;
     if (!raised) {
@@ -208,17 +333,35 @@ extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int
     return illm_launch_status();
 }
 
-// gated != 0: x [T, K] (x_dtype), w [E, 2 N, K], y [T * top, N] in the dtype of x; else x [T * top, K], w [E, N, K], y float32
+// gated != 0: x [T, K] (x_dtype), w [E, 2 N, K], y [T * top, N] in the dtype of x; else x [T * top, K], w [E, N, K], y float32.
+// tensor_cores != 0 (bfloat16, K % 8 == 0, tiles of 64 rows): the mma kernel.
 extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
-                             int act, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows,
-                             void* stream) {
+                             int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0,
+                             const int* tile_rows, void* stream) {
     if (T <= 0) return 0;
-    if (N <= 0 || K <= 0 || x_dtype != w_dtype) return ILLM_ERR_BAD_ARG;
-    const int bm = illm_moe_row_tile(T, top);
+    if (N <= 0 || K <= 0 || x_dtype != w_dtype || (bm != 16 && bm != 64)) return ILLM_ERR_BAD_ARG;
     const int tiles = illm_moe_max_tiles(T, top, E, bm);
     if (tiles > 65535) return ILLM_ERR_BAD_ARG;
-    dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
     cudaStream_t s = (cudaStream_t)stream;
+    if (tensor_cores) {
+        if (x_dtype != ILLM_BF16 || (K & 7) || bm != MM_BM || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ILLM_ERR_BAD_ARG;
+        dim3 mgrid((N + MM_BN - 1) / MM_BN, tiles);
+        const size_t smem = (size_t)MM_STAGES * (MM_BM + (gated ? 2 : 1) * MM_BN) * MM_LD * sizeof(bf16);
+        static bool raised = false;
+        if (!raised) {
+            cudaFuncSetAttribute(moe_gemm_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            cudaFuncSetAttribute(moe_gemm_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            raised = true;
+        }
+        if (gated)
+            illm_launch(moe_gemm_mma_kernel<bf16, true>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (bf16*)y, N, K, top, act,
+                        pair_of_row, tile_expert, tile_row0, tile_rows);
+        else
+            illm_launch(moe_gemm_mma_kernel<float, false>, mgrid, dim3(256), smem, s, (const bf16*)x, (const bf16*)w, (float*)y, N, K, top, act,
+                        pair_of_row, tile_expert, tile_row0, tile_rows);
+        return illm_launch_status();
+    }
+    dim3 grid((N + MOE_BN - 1) / MOE_BN, tiles);
 #define ILLM_MOE(TX, TY, BM, G)                                                                                                       \
     illm_launch(moe_gemm_kernel<TX, TX, TY, BM, G>, grid, dim3(256), 0, s, (const TX*)x, (const TX*)w, (TY*)y, N, K, top, act, pair_of_row, \
                 tile_expert, tile_row0, tile_rows)

@@ -81,6 +81,9 @@ public:
     // the library (cuBLAS), as the reference uses cublasSgemm for its float32 products
     // (src/kern/gpu/kernel_gpu.cu:420-435).
     void library_gemm_bf16(const void* x, const void* w, void* out, DType out_dtype, int M, int N, int K);
+    // `batch` products at once: out[:, b, :] = x[:, b, :] . w_b^T (transposed == false, w [batch * N, K]) or x[:, b, :] . w_b
+    // (transposed, w [batch * K, N]); x [M, batch * K] and out [M, batch * N] bfloat16 row-major.
+    void library_gemm_bf16_heads(const void* x, const void* w, void* out, int M, int N, int K, int batch, bool transposed);
 
     // Copy a small host array to the device without making the host wait for the work already queued:
     // through a ring of pinned staging buffers, each reused only when its copy has left.

@@ -732,6 +732,12 @@ Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transpo
         N = w.rows / heads;
     }
     Mat y = new_mat(dev, x.rows, (long long)heads * N, out_dtype);
+    // prompts in bfloat16: the library's batched product (a head per batch entry); few rows and float32: the kernel here
+    if (x.dtype == DType::BF16 && w.dtype == DType::BF16 && out_dtype == DType::BF16 && x.rows > kGemmTcMaxTokensAuto && K % 8 == 0 && N % 8 == 0 &&
+        !((uintptr_t)x.p & 15) && !((uintptr_t)w.p & 15)) {
+        dev.library_gemm_bf16_heads(x.p, w.p, y.p, (int)x.rows, (int)N, (int)K, heads, transposed);
+        return y;
+    }
     const int rc = illm_head_gemm(x.p, code_of(x.dtype, "head_linear"), w.p, code_of(w.dtype, "head_linear"), y.p, code_of(out_dtype, "head_linear"),
                                   (int)x.rows, heads, (int)N, (int)K, transposed ? 1 : 0, dev.stream());
     if (rc == 10001) throw KernelError("head_linear: this combination of dtypes is not supported");
@@ -748,7 +754,10 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
         w_down.rows != (long long)E * D)
         throw KernelError("moe: the experts' matrices do not match the input");
     const long long F = w_down.cols, P = T * top;
-    const int tiles = illm_moe_max_tiles((int)T, top, E, illm_moe_row_tile((int)T, top));
+    // bfloat16 with rows of whole 16-byte pieces runs on tensor cores; float32 (and odd sizes) on the plain kernel
+    const int tc = h.dtype == DType::BF16 && D % 8 == 0 && F % 8 == 0 ? 1 : 0;
+    const int bm = illm_moe_row_tile((int)T, top, tc);
+    const int tiles = illm_moe_max_tiles((int)T, top, E, bm);
     int* expert = dev.alloc_n<int>((size_t)P);
     float* weight = dev.alloc_n<float>((size_t)P);
     int* row_of_pair = dev.alloc_n<int>((size_t)P);
@@ -756,15 +765,15 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
     int* tile_expert = dev.alloc_n<int>((size_t)tiles);
     int* tile_row0 = dev.alloc_n<int>((size_t)tiles);
     int* tile_rows = dev.alloc_n<int>((size_t)tiles);
-    check_kernel(illm_moe_route((const float*)logits.p, router_bias, (int)T, E, top, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0,
+    check_kernel(illm_moe_route((const float*)logits.p, router_bias, (int)T, E, top, bm, expert, weight, row_of_pair, pair_of_row, tile_expert, tile_row0,
                                 tile_rows, dev.stream()),
                  "moe_route");
     const int code = code_of(h.dtype, "moe");
     Mat hid = new_mat_exact(dev, P, F, h.dtype), rows = new_mat_exact(dev, P, D, DType::F32), out = new_mat_exact(dev, T, D, DType::F32);
-    check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)F, (int)D, 1, act, pair_of_row, tile_expert, tile_row0, tile_rows,
+    check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)F, (int)D, 1, act, bm, tc, pair_of_row, tile_expert, tile_row0, tile_rows,
                                dev.stream()),
                  "moe_gemm (gate/up)");
-    check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, pair_of_row, tile_expert, tile_row0, tile_rows,
+    check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, bm, tc, pair_of_row, tile_expert, tile_row0, tile_rows,
                                dev.stream()),
                  "moe_gemm (down)");
     check_kernel(illm_moe_combine((const float*)rows.p, row_of_pair, weight, (float*)out.p, (int)T, (int)D, top, dev.stream()), "moe_combine");

@@ -77,7 +77,8 @@ struct LatentAttention : Mixer {
         if (kv.n_kv_heads != 1 || kv.head_dim != kv_rank) throw EngineError("latent_attention: the cache entry does not hold this layer's latent");
         Mat x = ops::linear(dev, rt->gemm, h, w_down, DType::F32, false).m;
         Mat cq = ops::latent_prep(dev, x, q_rank, kv_rank, (const float*)n_q.m.p, (const float*)n_kv.m.p, norm_eps, ctx, kv, rt->dtype);
-        Mat q = ops::linear(dev, rt->gemm, cq, w_uq.m, DType::F32, false).m;
+        // a prompt's queries are rounded to the activation dtype for the library's batched product; single tokens stay float32
+        Mat q = ops::linear(dev, rt->gemm, cq, w_uq.m, ctx.is_decode ? DType::F32 : rt->dtype, false).m;
         Mat qa = ops::head_linear(dev, q, w_uk.m, n_heads, true, rt->dtype);          // U_k,h^T q_h
         const ops::Geometry g{n_heads, 1, kv_rank};
         ops::AttentionExtras ex;

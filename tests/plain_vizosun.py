@@ -283,7 +283,9 @@ def random_weights(cfg, seed, scale=1.0):
     rng = np.random.default_rng(seed)
     w = {}
     for name, (shape, kind) in tensor_shapes(cfg).items():
-        if kind == "matrix":
+        if name in ("embed", "bigram"):
+            a = rng.standard_normal(shape)
+        elif kind == "matrix":
             a = rng.standard_normal(shape) * scale / math.sqrt(shape[-1])
         elif kind == "norm":
             a = 1.0 + 0.1 * rng.standard_normal(shape)

@@ -67,7 +67,7 @@ def test_feed_forward_part(dtype):
     ref = plain.swiglu_ffn(f64(x), f64(ws["gate_proj.weight"]), f64(ws["up_proj.weight"]), f64(ws["down_proj.weight"]))
     assert rel_err(f64(out), ref) <= TOL[dtype]
     with pytest.raises(ConfigError, match="activation"):
-        h.build("feed_forward", PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "relu"}))
+        h.build("feed_forward", PartSpec("gated_mlp", {"hidden_size": 8, "intermediate_size": 8, "activation": "softsign"}))
 
 
 def _attention(h, H, nh, nkv, d, window, theta, rot=None):

@@ -12,7 +12,7 @@ import os
 import numpy as np
 import pytest
 import plain_vizosun as pz
-from util import assert_close, rel_err
+from util import BF16_TOL, assert_close, rel_err
 
 from inferllm_b200 import Engine, EngineOptions, Model, ModelConfig, StepItem
 
@@ -21,12 +21,13 @@ pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
 
 
-def write_model(folder, cfg, seed, edit=None):
-    """config.json + model.safetensors (bfloat16) with random weights; returns the weights."""
-    w = pz.random_weights(cfg, seed)
+def write_model(folder, cfg, seed, edit=None, gain=0.5):
+    """config.json + model.safetensors (bfloat16) with random weights; returns the weights.  `gain` scales the
+    matrices: with larger ones a stack of layers amplifies rounding until bfloat16 decides the result."""
+    w = pz.random_weights(cfg, seed, gain)
     for name in w:
         if name.endswith("router"):
-            w[name] = pz.bf16_round(w[name] * 6.0)          # spread logits: the choice of experts is clear
+            w[name] = pz.bf16_round(w[name] * 6.0 / gain)   # spread logits: the choice of experts is clear
         if name.endswith("A_log"):
             w[name] = pz.bf16_round(np.linspace(-6.0, 0.5, w[name].size).astype(np.float32))     # slow and fast heads
     if edit:
@@ -62,13 +63,30 @@ def in_portions(eng, ids, sizes):
     return np.concatenate(out)
 
 
+def close(got, ref, dtype, what):
+    """float32: every position within the bound.  bfloat16: a router whose two best logits lie closer together than
+    the rounding of its input may choose the other expert, which changes that token's row (and, less, the rows after
+    it) by more than rounding: at most one position in fifty (or one) may exceed the bound, none five times the
+    bound, and the others are held to it."""
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    if dtype == "float32" or got.ndim < 2:
+        return assert_close(got, ref, dtype, what)
+    assert np.isfinite(got).all(), f"{what}: non-finite values"
+    err = np.abs(got - ref).max(-1) / max(np.abs(ref).max(), 1e-30)
+    over = err > BF16_TOL
+    assert over.sum() <= max(1, len(err) // 50), f"{what}: {int(over.sum())} of {len(err)} positions exceed {BF16_TOL:.1e} (worst {err.max():.3e})"
+    assert err.max() <= 5 * BF16_TOL, f"{what}: a position is off by {err.max():.3e}"
+    if (~over).any():
+        assert_close(got[~over], ref[~over], dtype, what)
+
+
 def same_or_close(a, b, dtype, what):
     """float32: every kernel fixes the order of its sums per row, so two ways of cutting the same tokens give
     the same bits; bfloat16: the library's products choose kernels by shape."""
     if dtype == "float32":
         assert np.array_equal(a, b), f"{what}: float32 logits differ between two cuttings (max {np.abs(a - b).max():.3e})"
     else:
-        assert rel_err(a, b) <= 4e-2, what
+        close(a, b, dtype, what)
 
 
 D, L = "channel_delta", "latent_attention"
@@ -140,7 +158,7 @@ def test_mechanism_alone(tmp_path, name, dtype):
 def test_whole_prompt(models, name, dtype):
     d, cfg, w = models[name]
     ids = prompt(cfg, 150, 11)
-    assert_close(whole(engine(d, dtype), ids), pz.forward(cfg, w, ids), dtype, name)
+    close(whole(engine(d, dtype), ids), pz.forward(cfg, w, ids), dtype, name)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -163,10 +181,10 @@ def test_portions_and_decoding(models, name, dtype):
     ref = pz.forward(cfg, w, ids)
     eng = engine(d, dtype)
     base = whole(eng, ids)
-    assert_close(base, ref, dtype, name)
+    close(base, ref, dtype, name)
     for sizes in ([1], [2], [63, 2, 64, 7], [128, 1], [5, 64, 3]):
         got = in_portions(eng, ids, sizes)
-        assert_close(got, ref, dtype, f"{name} portions {sizes}")
+        close(got, ref, dtype, f"{name} portions {sizes}")
         same_or_close(got, base, dtype, f"{name} portions {sizes}")
 
 
@@ -182,23 +200,25 @@ def test_unequal_batches(models, name, dtype):
     alone = [whole(eng, s) for s in seqs]
     slots = [eng.new_sequence() for _ in seqs]
     lg = eng.step([StepItem(slots[i], seqs[i][:lens[i]], list(range(lens[i]))) for i in range(len(seqs))]).cpu().numpy()
-    at = 0
+    at, got = 0, []
     for i, n in enumerate(lens):
-        assert_close(lg[at:at + n], refs[i][:n], dtype, f"{name} batch prompt {i}")
-        same_or_close(lg[at:at + n], alone[i][:n], dtype, f"{name} batch prompt {i}")
+        got.append([lg[at:at + n]])
         at += n
     pos = list(lens)
     live = list(range(len(seqs)))
     while live:
         lg = eng.step([StepItem(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu().numpy()
         for r, i in enumerate(live):
-            assert_close(lg[r], refs[i][pos[i]], dtype, f"{name} batch decode {i} at {pos[i]}")
-            same_or_close(lg[r], alone[i][pos[i]], dtype, f"{name} batch decode {i} at {pos[i]}")
+            got[i].append(lg[r:r + 1])
             pos[i] += 1
         for i in list(live):
             if pos[i] == len(seqs[i]):
                 eng.end_sequence(slots[i])
                 live.remove(i)
+    for i in range(len(seqs)):
+        g = np.concatenate(got[i])
+        close(g, refs[i], dtype, f"{name} batch, sequence {i}")
+        same_or_close(g, alone[i], dtype, f"{name} batch, sequence {i} against itself alone")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -215,11 +235,11 @@ def test_slots_and_pages_used_again(models, dtype):
         late = prompt(cfg, 40, 90 + rnd)
         s_late = eng.new_sequence()
         got_late = eng.step([StepItem(s_late, late, list(range(40)))]).cpu().numpy()
-        assert_close(got_late, pz.forward(cfg, w, late), dtype, f"round {rnd}: a sequence in a slot used before")
+        close(got_late, pz.forward(cfg, w, late), dtype, f"round {rnd}: a sequence in a slot used before")
         for i in (0, 2):
             rest = seqs[i][cut[i]:]
             got = eng.step([StepItem(slots[i], rest, list(range(len(rest))))]).cpu().numpy()
-            assert_close(got, pz.forward(cfg, w, seqs[i])[cut[i]:], dtype, f"round {rnd}: sequence {i} continued")
+            close(got, pz.forward(cfg, w, seqs[i])[cut[i]:], dtype, f"round {rnd}: sequence {i} continued")
             eng.end_sequence(slots[i])
         eng.end_sequence(s_late)
 
@@ -301,8 +321,14 @@ def test_greedy_generation(models, dtype):
     want = [pz.greedy_generate(cfg, w, p, 12) for p in prompts]
     if dtype == "float32":
         assert got == want
-    else:       # bfloat16 may turn a near-tie; the first tokens of every request must agree
-        assert all(g[0] == x[0] for g, x in zip(got, want)) and sum(g == x for g, x in zip(got, want)) >= len(want) - 1, (got, want)
+        return
+    # bfloat16 may turn a near-tie: every token the engine chose must be (within rounding) the best continuation of what
+    # it had generated so far, by the plain implementation's logits for that very sequence
+    for p, g in zip(prompts, got):
+        assert len(g) == 12
+        lg = pz.forward(cfg, w, p + g)[len(p) - 1:-1]
+        gap = lg.max(-1) - lg[np.arange(12), g]
+        assert (gap <= BF16_TOL * np.abs(lg).max()).all(), (g, gap)
 
 
 def test_trace_replay_program(models, tmp_path):
