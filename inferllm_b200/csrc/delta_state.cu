@@ -13,8 +13,8 @@
 // after the preparation has read them.  Everything here is float32 in both modes of the engine.
 //
 // delta_scan_kernel: the columns of S never meet, so a block owns (sequence, head, a group of columns); a column's
-// d rows are spread over L lanes (L the smallest power of two that leaves a thread at most 32 rows) and live in
-// registers for the whole step.  The step's tokens are staged through shared memory in tiles.  The two dot
+// d rows are spread over L lanes (L the smallest power of two that leaves a thread at most 32 rows; heads of up to
+// 512 key channels) and live in registers for the whole step.  The step's tokens are staged through shared memory in tiles.  The two dot
 // products of a token are added over the L lanes by a fixed tree of shuffles, and a token's arithmetic does not
 // depend on where the step's cut falls, so prompts, portions and single tokens give the same bits.
 #include "common.cuh"
@@ -109,12 +109,15 @@ __global__ void conv_state_kernel(DeltaArgs p) {
     }
 }
 
-// grid (column groups, heads, sequences); L lanes per column, DL_THREADS / L columns per block
+// grid (column groups, heads, sequences); L lanes per column, DL_THREADS / L columns per block.  A thread's 32 rows are
+// the quads 4 (l + L r) .. + 3 for r = 0..7, so that its q, k and g come as 16-byte reads of shared memory that the
+// lanes of a column make side by side; rows beyond d are padding (k = q = 0, so their state stays 0).  The two dot
+// products run as four chains each.
 template <int L>
 __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     pdl_grid_sync();
-    extern __shared__ float sm[];
-    constexpr int COLS = DL_THREADS / L;
+    extern __shared__ __align__(16) float sm[];
+    constexpr int COLS = DL_THREADS / L, DPAD = DL_ROWS * L;
     const int b = blockIdx.z, h = blockIdx.y, hk = h / (p.nh / p.nkv);
     const int d = p.d, dv = p.dv;
     const int l = threadIdx.x % L, jc = threadIdx.x / L;
@@ -126,75 +129,108 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     float S[DL_ROWS];
 #pragma unroll
     for (int r = 0; r < DL_ROWS; r++) {
-        const int i = l + L * r;
+        const int i = 4 * (l + L * (r >> 2)) + (r & 3);
         S[r] = (live && i < d) ? S_col[i] : 0.f;
     }
-    // a tile of tokens in shared memory: q, k, g [tile, d] each, v [tile, COLS], beta [tile]
+    // a tile of tokens in shared memory: q, k, g [tile, DPAD] each, v [tile, COLS], beta [tile]
     float* sq = sm;
-    float* sk = sq + DL_TILE * d;
-    float* sg = sk + DL_TILE * d;
-    float* sv = sg + DL_TILE * d;
+    float* sk = sq + DL_TILE * DPAD;
+    float* sg = sk + DL_TILE * DPAD;
+    float* sv = sg + DL_TILE * DPAD;
     float* sb = sv + DL_TILE * COLS;
     const int j0 = blockIdx.x * COLS;
+    const float* __restrict__ qkv = p.qkv;
+    const float* __restrict__ gg = p.g;
+    float* __restrict__ out = p.out;
     for (int t0 = 0; t0 < n; t0 += DL_TILE) {
         const int nt = min(DL_TILE, n - t0);
         __syncthreads();
-        for (int e = threadIdx.x; e < nt * d; e += DL_THREADS) {
-            const int tt = e / d, i = e - tt * d;
-            const size_t t = (size_t)(first + t0 + tt);
-            sq[e] = p.qkv[t * C + (size_t)hk * d + i];
-            sk[e] = p.qkv[t * C + nq + (size_t)hk * d + i];
-            sg[e] = p.g[t * p.nh * d + (size_t)h * d + i];
+        // the loads of a group of pieces first, then their stores: the reads are in flight together
+        constexpr int PIECES = DL_TILE * DPAD / DL_THREADS, GROUP = PIECES < 8 ? PIECES : 8;
+#pragma unroll 1
+        for (int e0 = 0; e0 < PIECES; e0 += GROUP) {
+            float rq[GROUP], rk[GROUP], rg[GROUP];
+#pragma unroll
+            for (int u = 0; u < GROUP; u++) {
+                const int e = (e0 + u) * DL_THREADS + threadIdx.x;
+                const int tt = e / DPAD, i = e % DPAD;
+                const size_t t = (size_t)(first + t0 + tt);
+                const bool in = i < d && tt < nt;
+                rq[u] = in ? __ldg(qkv + t * C + (size_t)hk * d + i) : 0.f;
+                rk[u] = in ? __ldg(qkv + t * C + nq + (size_t)hk * d + i) : 0.f;
+                rg[u] = in ? __ldg(gg + t * p.nh * d + (size_t)h * d + i) : 1.f;
+            }
+#pragma unroll
+            for (int u = 0; u < GROUP; u++) {
+                const int e = (e0 + u) * DL_THREADS + threadIdx.x;
+                sq[e] = rq[u];
+                sk[e] = rk[u];
+                sg[e] = rg[u];
+            }
         }
         for (int e = threadIdx.x; e < nt * COLS; e += DL_THREADS) {
             const int tt = e / COLS, c = e - tt * COLS;
-            sv[e] = j0 + c < dv ? p.qkv[(size_t)(first + t0 + tt) * C + 2 * nq + (size_t)h * dv + j0 + c] : 0.f;
+            sv[e] = j0 + c < dv ? __ldg(qkv + (size_t)(first + t0 + tt) * C + 2 * nq + (size_t)h * dv + j0 + c) : 0.f;
         }
-        for (int e = threadIdx.x; e < nt; e += DL_THREADS) sb[e] = p.beta[(size_t)(first + t0 + e) * p.nh + h];
+        for (int e = threadIdx.x; e < nt; e += DL_THREADS) sb[e] = __ldg(p.beta + (size_t)(first + t0 + e) * p.nh + h);
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float *q = sq + tt * d, *k = sk + tt * d, *g = sg + tt * d;
-            float acc = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DPAD);
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DPAD);
+            const float4* g4 = reinterpret_cast<const float4*>(sg + tt * DPAD);
+            float4 kk[DL_ROWS / 4];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < DL_ROWS; r++) {
-                const int i = l + L * r;
-                if (i < d) {
-                    S[r] *= g[i];
-                    acc = fmaf(k[i], S[r], acc);
-                }
+            for (int r = 0; r < DL_ROWS / 4; r++) {
+                const float4 g = g4[l + L * r];
+                kk[r] = k4[l + L * r];
+                S[4 * r] *= g.x;
+                S[4 * r + 1] *= g.y;
+                S[4 * r + 2] *= g.z;
+                S[4 * r + 3] *= g.w;
+                a0 = fmaf(kk[r].x, S[4 * r], a0);
+                a1 = fmaf(kk[r].y, S[4 * r + 1], a1);
+                a2 = fmaf(kk[r].z, S[4 * r + 2], a2);
+                a3 = fmaf(kk[r].w, S[4 * r + 3], a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             const float u = sb[tt] * (sv[tt * COLS + jc] - acc);
-            float oacc = 0.f;
+            a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < DL_ROWS; r++) {
-                const int i = l + L * r;
-                if (i < d) {
-                    S[r] = fmaf(k[i], u, S[r]);
-                    oacc = fmaf(q[i], S[r], oacc);
-                }
+            for (int r = 0; r < DL_ROWS / 4; r++) {
+                const float4 q = q4[l + L * r];
+                S[4 * r] = fmaf(kk[r].x, u, S[4 * r]);
+                S[4 * r + 1] = fmaf(kk[r].y, u, S[4 * r + 1]);
+                S[4 * r + 2] = fmaf(kk[r].z, u, S[4 * r + 2]);
+                S[4 * r + 3] = fmaf(kk[r].w, u, S[4 * r + 3]);
+                a0 = fmaf(q.x, S[4 * r], a0);
+                a1 = fmaf(q.y, S[4 * r + 1], a1);
+                a2 = fmaf(q.z, S[4 * r + 2], a2);
+                a3 = fmaf(q.w, S[4 * r + 3], a3);
             }
+            float oacc = (a0 + a1) + (a2 + a3);
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, o);
-            if (live && l == 0) p.out[(size_t)(first + t0 + tt) * p.nh * dv + (size_t)h * dv + j] = oacc;
+            if (live && l == 0) out[(size_t)(first + t0 + tt) * p.nh * dv + (size_t)h * dv + j] = oacc;
         }
     }
     if (live) {
 #pragma unroll
         for (int r = 0; r < DL_ROWS; r++) {
-            const int i = l + L * r;
+            const int i = 4 * (l + L * (r >> 2)) + (r & 3);
             if (i < d) S_col[i] = S[r];
         }
     }
 }
 
-extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 1 && d <= 32 * DL_ROWS && dv >= 1 && taps >= 1 && taps <= 64; }
+extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 1 && d <= 16 * DL_ROWS && dv >= 1 && taps >= 1 && taps <= 64; }
 
 template <int L>
 static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
     constexpr int COLS = DL_THREADS / L;
-    const size_t smem = (size_t)(DL_TILE * (3 * p.d + COLS + 1)) * sizeof(float);
+    const size_t smem = (size_t)(DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
     static bool raised = false;
     if (!raised) {
         cudaFuncSetAttribute(delta_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -215,7 +251,7 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     if (!illm_delta_rule_supported(d, dv, taps) || nkv <= 0 || nh % nkv) return ILLM_ERR_BAD_ARG;
     const long long C = 2LL * nkv * d + (long long)nh * dv;
     if (state_elems < (long long)nh * d * dv + (taps - 1) * C) return ILLM_ERR_BAD_ARG;
-    if (C * sizeof(float) > 200 * 1024 || (size_t)(DL_TILE * (3 * d + DL_THREADS + 1)) * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
+    if (C * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     DeltaArgs p;
     p.x = x; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off;
@@ -234,7 +270,6 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     else if (d <= 64) launch_scan<2>(p, B, s);
     else if (d <= 128) launch_scan<4>(p, B, s);
     else if (d <= 256) launch_scan<8>(p, B, s);
-    else if (d <= 512) launch_scan<16>(p, B, s);
-    else launch_scan<32>(p, B, s);
+    else launch_scan<16>(p, B, s);
     return illm_launch_status();
 }
