@@ -519,6 +519,9 @@ def main():
     args = ap.parse_args()
 
     if args.design:
+        if args.no_pdl:       # every kernel's record then is its own time (no wait for the kernel before it inside it)
+            from inferllm_b200.kernels import ops as _ops
+            _ops.set_pdl(False)
         return run_design(args)
     if args.gpus != 1:
         print(f"bench.py: inferllm_b200 is a single-GPU library; --gpus {args.gpus} is not supported (N=1 only)")

@@ -230,7 +230,24 @@ extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 
 template <int L>
 static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
     constexpr int COLS = DL_THREADS / L;
-    const size_t smem = (size_t)(DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
+    size_t smem = (size_t)(DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
+    // The scan is bound by what an SM's shared memory delivers per clock, so its blocks must spread over the SMs.  Launched
+    // behind kernels that still hold most SMs, a small grid would be packed onto the few SMs that are free first (measured: 32
+    // blocks, 2.5 ms instead of 0.95 ms).  Asking for more shared memory than the tiles need caps the blocks per SM at what an
+    // even spread gives.
+    static int n_sms = 0;
+    if (!n_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (n_sms <= 0) n_sms = 1;
+    }
+    const long long blocks = (long long)((p.dv + COLS - 1) / COLS) * p.nh * B;
+    const long long per_sm = (blocks + n_sms - 1) / n_sms;
+    if (per_sm < 5) {
+        const size_t spread = (size_t)(220 * 1024) / (size_t)per_sm - 2048;
+        smem = smem > spread ? smem : (spread < (size_t)200 * 1024 ? spread : (size_t)200 * 1024);
+    }
     static bool raised = false;
     if (!raised) {
         cudaFuncSetAttribute(delta_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
