@@ -55,7 +55,11 @@ int illm_moe_max_tiles(int T, int top, int E, int bm);
 int illm_moe_row_tile(int T, int top, int tensor_cores);
 int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair, int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream);
 int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated, int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0, const int* tile_rows, void* stream);
+int illm_moe_gather_rows(const void* x, void* xs, const int* pair_of_row, int P, int K, int top, void* stream);
 int illm_moe_combine(const float* rows, const int* row_of_pair, const float* weight, float* out, int T, int D, int top, void* stream);
+
+// moe_tc.cu
+int illm_moe_gemm_tc(const void* xs, const void* w, void* y, int P, int E, int N, int K, int gated, int act, int tiles, const int* tile_expert, const int* tile_row0, const int* tile_rows, int* err, void* stream);
 
 // stream_ops.cu
 int illm_gated_act(const void* gu, void* out, int act_dtype, int T, int I, int act, void* stream);

@@ -5,9 +5,9 @@
 //                      equal values), softmax over the chosen -> expert [T, top], weight [T, top]
 //   moe_layout_kernel  one block: rows per expert, their offsets, the (token, choice) pairs placed expert by expert
 //                      (row_of_pair, pair_of_row), and the list of row tiles (tile -> expert, first row, rows)
-//   moe_gemm_kernel    one block per (row tile, 64 output columns): rows of one expert against that expert's
-//                      matrix; GATED: hid = act(x W_gate^T) * (x W_up^T) with x gathered by token; else the down
-//                      product into float32 rows.  One chain of fused multiply-adds over the inner index per
+//   moe_gemm_kernel    one block per (row tile, 64 columns): rows of one expert against that expert's matrix; GATED:
+//                      the matrix's rows 2i, 2i + 1 are gate and up of output i (packed so at load), x is gathered by
+//                      token and hid = act(gate) * up; else the down product into float32 rows.  One chain of fused multiply-adds over the inner index per
 //                      output, so a row's bits depend neither on its place among the rows nor on the step.
 //   moe_combine_kernel out[t] = sum over the choices, in their order, of weight * row
 //
@@ -96,18 +96,18 @@ __device__ __forceinline__ float moe_act(float v, int act) {
 #define MOE_BN 64
 #define MOE_BK 16
 
-// grid (ceil(N / 64), max_tiles); 256 threads = 16 x 16, a (BM / 16) x 4 patch of outputs each.
-// GATED: x [T, K] gathered through pair_of_row / top, w [E, 2 N, K] (an expert's gate rows, then its up rows), y [P, N];
-// else x [P, K] by row, w [E, N, K], y [P, N].
+// grid (ceil(Nw / 64), max_tiles); 256 threads = 16 x 16, a (BM / 16) x 4 patch of outputs each.  w [E, Nw, K].
+// GATED: x [T, K] gathered through pair_of_row / top; the matrix's rows 2i, 2i + 1 are gate and up of output i, and
+// y [P, Nw / 2] = act(gate) * up; else x [P, K] by row and y [P, Nw].
 template <typename TX, typename TW, typename TY, int BM, bool GATED>
 __global__ void __launch_bounds__(256)
-moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int N, int K, int top, int act,
+moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int Nw, int K, int top, int act,
                 const int* __restrict__ pair_of_row, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                 const int* __restrict__ tile_rows) {
     pdl_grid_sync();
     constexpr int RM = BM / 16;
     __shared__ float xs[MOE_BK][BM + 4];
-    __shared__ float ws[GATED ? 2 : 1][MOE_BK][MOE_BN + 4];
+    __shared__ float ws[MOE_BK][MOE_BN + 4];
     __shared__ int src_row[BM];
     const int tile = blockIdx.y;
     const int rows = tile_rows[tile];
@@ -115,16 +115,12 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
     const int e = tile_expert[tile], row0 = tile_row0[tile], n0 = blockIdx.x * MOE_BN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
     for (int m = threadIdx.x; m < BM; m += 256) src_row[m] = m < rows ? (GATED ? pair_of_row[row0 + m] / top : row0 + m) : -1;
-    const TW* wg = w + (size_t)e * (GATED ? 2 : 1) * N * K;
-    const TW* wu = wg + (size_t)N * K;
-    float acc[RM][4], acu[GATED ? RM : 1][4];
+    const TW* we = w + (size_t)e * Nw * K;
+    float acc[RM][4];
 #pragma unroll
     for (int i = 0; i < RM; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            acc[i][j] = 0.f;
-            if (GATED) acu[i][j] = 0.f;
-        }
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
     __syncthreads();
     for (int k0 = 0; k0 < K; k0 += MOE_BK) {
         for (int el = threadIdx.x; el < BM * MOE_BK; el += 256) {
@@ -134,28 +130,20 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
         }
         for (int el = threadIdx.x; el < MOE_BN * MOE_BK; el += 256) {
             const int n = el / MOE_BK, k = el % MOE_BK;
-            const bool in = n0 + n < N && k0 + k < K;
-            ws[0][k][n] = in ? to_f32(wg[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
-            if (GATED) ws[1][k][n] = in ? to_f32(wu[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+            ws[k][n] = (n0 + n < Nw && k0 + k < K) ? to_f32(we[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < MOE_BK; k++) {
-            float a[RM], b[4], c[4];
+            float a[RM], b[4];
 #pragma unroll
             for (int i = 0; i < RM; i++) a[i] = xs[k][ty * RM + i];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                b[j] = ws[0][k][tx * 4 + j];
-                if (GATED) c[j] = ws[GATED ? 1 : 0][k][tx * 4 + j];
-            }
+            for (int j = 0; j < 4; j++) b[j] = ws[k][tx * 4 + j];
 #pragma unroll
             for (int i = 0; i < RM; i++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-                    if (GATED) acu[i][j] = fmaf(a[i], c[j], acu[i][j]);
-                }
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
         }
         __syncthreads();
     }
@@ -163,23 +151,28 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
     for (int i = 0; i < RM; i++) {
         const int m = ty * RM + i;
         if (m >= rows) continue;
+        if (GATED) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int n = n0 + tx * 4 + j;
-            if (n >= N) continue;
-            const float v = GATED ? moe_act(acc[i][j], act) * acu[i][j] : acc[i][j];
-            y[(size_t)(row0 + m) * N + n] = from_f32<TY>(v);
+            for (int j = 0; j < 4; j += 2) {
+                const int n = n0 + tx * 4 + j;
+                if (n + 1 < Nw) y[(size_t)(row0 + m) * (Nw / 2) + n / 2] = from_f32<TY>(moe_act(acc[i][j], act) * acc[i][j + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int n = n0 + tx * 4 + j;
+                if (n < Nw) y[(size_t)(row0 + m) * Nw + n] = from_f32<TY>(acc[i][j]);
+            }
         }
     }
 }
-
 
 // ---- the same product on tensor cores (bfloat16, K a multiple of 8)
 //
 // A 64 x 128 tile per block, 8 warps of 32 x 32, K in slabs of 32 through a ring of three shared-memory stages filled
 // by cp.async (rows padded to 80 bytes, so that ldmatrix reads without bank conflicts); rows of the tile beyond the
-// expert's rows and columns beyond N are zero-filled on the way in and masked on the way out.  GATED keeps two
-// accumulators (gate and up) and stores act(gate) * up.
+// expert's rows and columns beyond N are zero-filled on the way in and masked on the way out.  GATED: the matrix's
+// rows 2i, 2i + 1 are gate and up of output i, which neighbouring accumulator columns of a thread hold.
 #define MM_BM 64
 #define MM_BN 128
 #define MM_BK 32
@@ -206,7 +199,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* 
                     const int* __restrict__ tile_rows) {
     pdl_grid_sync();
     extern __shared__ __align__(16) unsigned char mm_raw[];
-    constexpr int NB = GATED ? 2 : 1;
+    constexpr int NB = 1;
     constexpr int A_ELEMS = MM_BM * MM_LD, B_ELEMS = MM_BN * MM_LD, STAGE_ELEMS = A_ELEMS + NB * B_ELEMS;
     bf16* sm = reinterpret_cast<bf16*>(mm_raw);
     __shared__ int src_row[MM_BM];
@@ -217,7 +210,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = warp >> 2, wn = warp & 3;
     for (int m = tid; m < MM_BM; m += 256) src_row[m] = m < rows ? (GATED ? pair_of_row[row0 + m] / top : row0 + m) : -1;
     __syncthreads();
-    const bf16* wg = w + (size_t)e * NB * N * K;
+    const bf16* wg = w + (size_t)e * N * K;
     const int KT = (K + MM_BK - 1) / MM_BK;
     // what this thread copies per slab: one 16-byte piece of A, two of each B
     const int a_r = tid >> 2, a_c = (tid & 3) * 8;
@@ -289,12 +282,15 @@ moe_gemm_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* 
 #pragma unroll
         for (int j = 0; j < 4; j++)
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
+            for (int c = 0; c < 4; c += GATED ? 2 : 1) {
                 const int m = wm * 32 + i * 16 + (lane >> 2) + (c >> 1) * 8;
                 const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + (c & 1);
-                if (m >= rows || n >= N) continue;
-                const float v = GATED ? moe_act(acc[0][i][j][c], act) * acc[NB - 1][i][j][c] : acc[0][i][j][c];
-                y[(size_t)(row0 + m) * N + n] = from_f32<TY>(v);
+                if (m >= rows) continue;
+                if (GATED) {          // columns n, n + 1 are gate and up of output n / 2
+                    if (n + 1 < N) y[(size_t)(row0 + m) * (N / 2) + n / 2] = from_f32<TY>(moe_act(acc[0][i][j][c], act) * acc[0][i][j][c + 1]);
+                } else if (n < N) {
+                    y[(size_t)(row0 + m) * N + n] = from_f32<TY>(acc[0][i][j][c]);
+                }
             }
 }
 
@@ -314,12 +310,27 @@ extern "C" int illm_moe_max_tiles(int T, int top, int E, int bm) { return (int)(
 // rows per tile: the tensor-core kernel takes 64; the plain one 16 for steps of few tokens, else 64
 extern "C" int illm_moe_row_tile(int T, int top, int tensor_cores) { return tensor_cores || (long long)T * top > 1024 ? 64 : 16; }
 
+// xs[row, :] = x[pair_of_row[row] / top, :], 16 bytes at a time (K a multiple of 8): the rows in the experts' order
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, bf16* __restrict__ xs, const int* __restrict__ pair_of_row, int K, int top) {
+    pdl_grid_sync();
+    const int row = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair_of_row[row] / top) * K);
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * K);
+    for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = src[c];
+}
+extern "C" int illm_moe_gather_rows(const void* x, void* xs, const int* pair_of_row, int P, int K, int top, void* stream) {
+    if (P <= 0) return 0;
+    if (K & 7) return ILLM_ERR_BAD_ARG;
+    illm_launch(moe_gather_rows_kernel, dim3(P), dim3(128), 0, (cudaStream_t)stream, (const bf16*)x, (bf16*)xs, pair_of_row, K, top);
+    return illm_launch_status();
+}
+
 // logits [T, E] float32 (without the bias); expert, weight [T, top]; row_of_pair, pair_of_row [T * top];
 // tile_* [illm_moe_max_tiles(T, top, E, bm)], bm = illm_moe_row_tile(..)
 extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int E, int top, int bm, int* expert, float* weight, int* row_of_pair,
                               int* pair_of_row, int* tile_expert, int* tile_row0, int* tile_rows, void* stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E || (bm != 16 && bm != 64) || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || top > E || (bm != 16 && bm != 64 && bm != 128) || (size_t)(3 * E + 1) * sizeof(int) > 160 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     illm_launch(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, s, logits, bias, T, E, top, expert, weight);
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
@@ -333,20 +344,21 @@ extern "C" int illm_moe_route(const float* logits, const float* bias, int T, int
     return illm_launch_status();
 }
 
-// gated != 0: x [T, K] (x_dtype), w [E, 2 N, K], y [T * top, N] in the dtype of x; else x [T * top, K], w [E, N, K], y float32.
+// w [E, N, K].  gated != 0: x [T, K] (x_dtype), the matrix's rows 2i, 2i + 1 gate and up of output i, y [T * top, N / 2] in
+// the dtype of x; else x [T * top, K], y [T * top, N] float32.
 // tensor_cores != 0 (bfloat16, K % 8 == 0, tiles of 64 rows): the mma kernel.
 extern "C" int illm_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int T, int top, int E, int N, int K, int gated,
                              int act, int bm, int tensor_cores, const int* pair_of_row, const int* tile_expert, const int* tile_row0,
                              const int* tile_rows, void* stream) {
     if (T <= 0) return 0;
-    if (N <= 0 || K <= 0 || x_dtype != w_dtype || (bm != 16 && bm != 64)) return ILLM_ERR_BAD_ARG;
+    if (N <= 0 || K <= 0 || x_dtype != w_dtype || (bm != 16 && bm != 64) || (gated && (N & 1))) return ILLM_ERR_BAD_ARG;
     const int tiles = illm_moe_max_tiles(T, top, E, bm);
     if (tiles > 65535) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (tensor_cores) {
         if (x_dtype != ILLM_BF16 || (K & 7) || bm != MM_BM || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ILLM_ERR_BAD_ARG;
         dim3 mgrid((N + MM_BN - 1) / MM_BN, tiles);
-        const size_t smem = (size_t)MM_STAGES * (MM_BM + (gated ? 2 : 1) * MM_BN) * MM_LD * sizeof(bf16);
+        const size_t smem = (size_t)MM_STAGES * (MM_BM + MM_BN) * MM_LD * sizeof(bf16);
         static bool raised = false;
         if (!raised) {
             cudaFuncSetAttribute(moe_gemm_mma_kernel<bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);

@@ -754,9 +754,11 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
         w_down.rows != (long long)E * D)
         throw KernelError("moe: the experts' matrices do not match the input");
     const long long F = w_down.cols, P = T * top;
-    // bfloat16 with rows of whole 16-byte pieces runs on tensor cores; float32 (and odd sizes) on the plain kernel
+    // bfloat16 with rows of whole 16-byte pieces runs on tensor cores: prompts on tcgen05 (tiles of 128 rows of the rows
+    // gathered into the experts' order), few rows on warp-level MMA; float32 (and odd sizes) on the plain kernel
     const int tc = h.dtype == DType::BF16 && D % 8 == 0 && F % 8 == 0 ? 1 : 0;
-    const int bm = illm_moe_row_tile((int)T, top, tc);
+    const bool tc5 = tc && P >= kMoeTcgen05MinRows;
+    const int bm = tc5 ? 128 : illm_moe_row_tile((int)T, top, tc);
     const int tiles = illm_moe_max_tiles((int)T, top, E, bm);
     int* expert = dev.alloc_n<int>((size_t)P);
     float* weight = dev.alloc_n<float>((size_t)P);
@@ -770,12 +772,23 @@ Mat moe_forward(Device& dev, const Mat& h, const Mat& logits, const float* route
                  "moe_route");
     const int code = code_of(h.dtype, "moe");
     Mat hid = new_mat_exact(dev, P, F, h.dtype), rows = new_mat_exact(dev, P, D, DType::F32), out = new_mat_exact(dev, T, D, DType::F32);
-    check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)F, (int)D, 1, act, bm, tc, pair_of_row, tile_expert, tile_row0, tile_rows,
-                               dev.stream()),
-                 "moe_gemm (gate/up)");
-    check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, bm, tc, pair_of_row, tile_expert, tile_row0, tile_rows,
-                               dev.stream()),
-                 "moe_gemm (down)");
+    if (tc5) {
+        Mat xs = new_mat_exact(dev, P, D, DType::BF16);
+        check_kernel(illm_moe_gather_rows(h.p, xs.p, pair_of_row, (int)P, (int)D, top, dev.stream()), "moe_gather_rows");
+        check_kernel(illm_moe_gemm_tc(xs.p, w_gu.p, hid.p, (int)P, E, (int)(2 * F), (int)D, 1, act, tiles, tile_expert, tile_row0, tile_rows,
+                                      dev.tc_error_word(), dev.stream()),
+                     "moe_gemm_tc (gate/up)");
+        check_kernel(illm_moe_gemm_tc(hid.p, w_down.p, rows.p, (int)P, E, (int)D, (int)F, 0, 0, tiles, tile_expert, tile_row0, tile_rows,
+                                      dev.tc_error_word(), dev.stream()),
+                     "moe_gemm_tc (down)");
+    } else {
+        check_kernel(illm_moe_gemm(h.p, code, w_gu.p, code, hid.p, (int)T, top, E, (int)(2 * F), (int)D, 1, act, bm, tc, pair_of_row, tile_expert, tile_row0,
+                                   tile_rows, dev.stream()),
+                     "moe_gemm (gate/up)");
+        check_kernel(illm_moe_gemm(hid.p, code, w_down.p, code, rows.p, (int)T, top, E, (int)D, (int)F, 0, 0, bm, tc, pair_of_row, tile_expert, tile_row0,
+                                   tile_rows, dev.stream()),
+                     "moe_gemm (down)");
+    }
     check_kernel(illm_moe_combine((const float*)rows.p, row_of_pair, weight, (float*)out.p, (int)T, (int)D, top, dev.stream()), "moe_combine");
     return out;
 }

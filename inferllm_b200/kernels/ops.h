@@ -84,6 +84,7 @@ constexpr int kLibraryRowBucket = 64;
 constexpr int kGemmTcMaxTokensAuto = 16;
 constexpr int kGatedPromptsOnTcMinTokens = 512;
 constexpr int kMaxHeadDimGeneric = 256;
+constexpr int kMoeTcgen05MinRows = 256;      // (token, expert) pairs from which a routed feed-forward's products run on tcgen05
 constexpr int kMaxNormWidth = 200 * 1024 / 4;
 constexpr int kDecodeChunk = 256, kGqaDecodeChunk = 128, kGqaDecodeMinGroup = 4, kRingDecodeMaxSplits = 32;
 
@@ -259,7 +260,7 @@ Mat latent_prep(Device& dev, const Mat& x_f32, int q_rank, int kv_rank, const fl
 Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype);
 
 // Routed feed-forward (csrc/moe.cu).  logits float32 [T, experts] without the bias.  w_gate_up [experts * 2 ff, hidden]
-// (per expert its gate rows, then its up rows), w_down [experts * hidden, ff].  Returns float32 [T, hidden].
+// (per expert, rows 2i and 2i + 1 are gate and up of output i), w_down [experts * hidden, ff].  Returns float32 [T, hidden].
 Mat moe_forward(Device& dev, const Mat& h, const Mat& logits_f32, const float* router_bias, int experts, int top, const Mat& w_gate_up,
                 const Mat& w_down, int act);
 

@@ -3,8 +3,9 @@
 //     z = W_r h (+ b_r)  [experts], float32;   the `top` experts with the largest z;   weights = softmax over the chosen z
 //     y = sum over the chosen experts of weight * W_down,e ( act(W_gate,e h) * (W_up,e h) )
 //
-// Experts have no biases.  Their matrices are packed at load: gate and up rows of an expert one after the other in
-// one [experts * 2 ff, hidden] matrix, the down matrices in one [experts * hidden, ff].  The tokens of a step are
+// Experts have no biases.  Their matrices are packed at load: gate and up rows of an expert in turn (row 2i the gate
+// row and row 2i + 1 the up row of output i, so that a product's epilogue can apply the activation) in one
+// [experts * 2 ff, hidden] matrix, the down matrices in one [experts * hidden, ff].  The tokens of a step are
 // grouped by expert on the device (nothing of the routing comes back to the host), so a step launches the same
 // kernels whatever the router decides.  Tensor names: `names` gives "router", "router_bias", the experts' prefix
 // "expert" (followed by the expert's number and a dot) and "gate", "up", "down" below it.
@@ -55,8 +56,8 @@ struct RoutedMLP : FeedForward {
         w_down = Mat{down_buf.get(), (long long)experts * hidden, inter, rt->dtype, (long long)experts * hidden};
         for (int e = 0; e < experts; e++) {
             char* gu = (char*)w_gate_up.p + (size_t)e * 2 * inter * hidden * es;
-            src.fetch_into(expert_tensor(e, "gate"), gu, rt->dtype);
-            src.fetch_into(expert_tensor(e, "up"), gu + (size_t)inter * hidden * es, rt->dtype);
+            src.fetch_into(expert_tensor(e, "gate"), gu, rt->dtype, 2 * hidden);              // rows 2i
+            src.fetch_into(expert_tensor(e, "up"), gu + (size_t)hidden * es, rt->dtype, 2 * hidden);  // rows 2i + 1
             src.fetch_into(expert_tensor(e, "down"), (char*)w_down.p + (size_t)e * hidden * inter * es, rt->dtype);
         }
     }
