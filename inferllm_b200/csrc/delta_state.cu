@@ -22,10 +22,11 @@
 #define DL_THREADS 128
 #define DL_ROWS 32
 #define DL_TILE 16
+#define DL_PREP_TOKENS 4
 
 struct DeltaArgs {
     const float* x;                 // [T, ld] the packed float32 projection
-    int ld, q_off, k_off, v_off, b_off;
+    int T, ld, q_off, k_off, v_off, b_off;
     const float* a;                 // [T, nh * d] decay projection (before the bias)
     int nh, nkv, d, dv, taps;
     const float *conv_q, *conv_k, *conv_v;      // [channels, taps]
@@ -42,49 +43,125 @@ struct DeltaArgs {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 
-// one block per token; dynamic shared memory: C floats
+// The convolution of one channel at token t: the taps oldest first (one chain of fused multiply-adds, the same whether a
+// row comes from the step or from the state), all inputs loaded before the chain starts.
+__device__ __forceinline__ float conv_channel(const DeltaArgs& p, int t, int i_step, int pos, int c, int col, const float* __restrict__ taps,
+                                              const float* __restrict__ conv_state, int C) {
+    const int K = p.taps;
+    float y = 0.f;
+    if (K <= 8) {
+        float in[8], w[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            in[j] = 0.f;
+            w[j] = 0.f;
+            if (j < K && pos - j >= 0) {
+                in[j] = j <= i_step ? __ldg(p.x + (size_t)(t - j) * p.ld + col) : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
+                w[j] = __ldg(taps + K - 1 - j);
+            }
+        }
+#pragma unroll
+        for (int j = 7; j >= 0; j--)
+            if (j < K && pos - j >= 0) y = fmaf(w[j], in[j], y);
+        return y;
+    }
+    for (int j = K - 1; j >= 0; j--) {
+        if (pos - j < 0) continue;
+        const float in = j <= i_step ? p.x[(size_t)(t - j) * p.ld + col] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
+        y = fmaf(taps[K - 1 - j], in, y);
+    }
+    return y;
+}
+
+// grid (tokens, units), 256 threads.  A unit is a group of query or key heads (convolution, silu, unit vectors; as many
+// heads as fit 256 threads, a head of more than 256 channels alone), a piece of 1024 value channels (convolution, silu),
+// a piece of 1024 decay channels, or the write strengths of all heads.
+__device__ __forceinline__ int delta_heads_per_block(int d) { return d > 256 ? 1 : 256 / ((d + 31) / 32 * 32); }
+
 __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
     pdl_grid_sync();
-    extern __shared__ float sm[];
-    const int t = blockIdx.x;
-    const int seq = p.token_seq[t], pos = p.token_pos[t];
-    const int first = p.cu_q[seq];                 // the step's first token of this sequence
-    const int i_step = t - first;
-    const int nq = p.nkv * p.d, nv = p.nh * p.dv, C = 2 * nq + nv, K = p.taps;
-    const float* conv_state = p.state + (size_t)p.slots[seq] * p.state_elems + (size_t)p.nh * p.d * p.dv;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float* taps;
-        int col;
-        if (c < nq) { taps = p.conv_q + (size_t)c * K; col = p.q_off + c; }
-        else if (c < 2 * nq) { taps = p.conv_k + (size_t)(c - nq) * K; col = p.k_off + c - nq; }
-        else { taps = p.conv_v + (size_t)(c - 2 * nq) * K; col = p.v_off + c - 2 * nq; }
-        float y = 0.f;
-        for (int j = K - 1; j >= 0; j--) {          // oldest input first
-            if (pos - j < 0) continue;
-            const float in = j <= i_step ? p.x[(size_t)(t - j) * p.ld + col] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
-            y = fmaf(taps[K - 1 - j], in, y);
-        }
-        sm[c] = silu_f(y);
-    }
+    __shared__ float scratch[32];
+    __shared__ float warp_ss[8];
+    const int unit = blockIdx.y;
+    // a block takes DL_PREP_TOKENS tokens in turn: the look-ups at the start of a token are a chain of dependent loads,
+    // which a block of one token would spend most of its life on
+#pragma unroll 1
+    for (int t = blockIdx.x * DL_PREP_TOKENS; t < min(p.T, (int)(blockIdx.x + 1) * DL_PREP_TOKENS); t++) {
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int seq = p.token_seq[t], pos = p.token_pos[t];
+    const int i_step = t - p.cu_q[seq];            // the token's place among the step's tokens of its sequence
+    const int d = p.d, nq = p.nkv * d, nv = p.nh * p.dv, ng = p.nh * d, C = 2 * nq + nv, K = p.taps;
+    const float* conv_state = p.state + (size_t)p.slots[seq] * p.state_elems + (size_t)p.nh * d * p.dv;
     float* dst = p.qkv + (size_t)t * C;
-    for (int hh = warp; hh < 2 * p.nkv; hh += n_warps) {          // unit vectors per query and key head
-        const float* v = sm + (size_t)hh * p.d;
-        float ss = 0.f;
-        for (int i = lane; i < p.d; i += 32) ss = fmaf(v[i], v[i], ss);
-        ss = warp_sum(ss);
-        const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (hh < p.nkv ? p.q_scale : 1.0f);
-        for (int i = lane; i < p.d; i += 32) dst[(size_t)hh * p.d + i] = v[i] * inv;
+    const int hpb = delta_heads_per_block(d), qk_units = (2 * p.nkv + hpb - 1) / hpb;
+    const int v_units = (nv + 1023) / 1024, g_units = (ng + 1023) / 1024;
+    if (unit < qk_units && d <= 256) {
+        // thread -> (head of the unit, channel); a head's sum of squares: its warps' sums added in order
+        const int dth = (d + 31) / 32 * 32, hl = threadIdx.x / dth, i = threadIdx.x % dth;
+        const int head = unit * hpb + hl;           // 0 .. nkv - 1 query heads, then the key heads
+        const bool live = hl < hpb && head < 2 * p.nkv && i < d;
+        const bool is_q = head < p.nkv;
+        const int hh = is_q ? head : head - p.nkv;
+        float v = 0.f;
+        if (live)
+            v = silu_f(conv_channel(p, t, i_step, pos, head * d + i, (is_q ? p.q_off : p.k_off) + hh * d + i,
+                                    (is_q ? p.conv_q : p.conv_k) + ((size_t)hh * d + i) * K, conv_state, C));
+        const float ws = warp_sum(v * v);
+        if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ws;
+        __syncthreads();
+        if (live) {
+            float ss = 0.f;
+            for (int w = hl * (dth / 32); w < (hl + 1) * (dth / 32); w++) ss += warp_ss[w];
+            dst[head * d + i] = v * ((1.0f / sqrtf(ss + 1e-6f)) * (is_q ? p.q_scale : 1.0f));
+        }
+    } else if (unit < qk_units) {
+        const bool is_q = unit < p.nkv;
+        const int hh = is_q ? unit : unit - p.nkv;
+        const float* taps = (is_q ? p.conv_q : p.conv_k) + (size_t)hh * d * K;
+        const int c0 = unit * d, col0 = (is_q ? p.q_off : p.k_off) + hh * d;
+        float v[2], ss = 0.f;                       // up to 512 channels per head
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int i = threadIdx.x + r * 256;
+            v[r] = 0.f;
+            if (i < d) {
+                v[r] = silu_f(conv_channel(p, t, i_step, pos, c0 + i, col0 + i, taps + (size_t)i * K, conv_state, C));
+                ss = fmaf(v[r], v[r], ss);
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = (1.0f / sqrtf(ss + 1e-6f)) * (is_q ? p.q_scale : 1.0f);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int i = threadIdx.x + r * 256;
+            if (i < d) dst[c0 + i] = v[r] * inv;
+        }
+    } else if (unit < qk_units + v_units) {
+        float y[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int c = (unit - qk_units) * 1024 + r * 256 + threadIdx.x;
+            y[r] = c < nv ? conv_channel(p, t, i_step, pos, 2 * nq + c, p.v_off + c, p.conv_v + (size_t)c * K, conv_state, C) : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int c = (unit - qk_units) * 1024 + r * 256 + threadIdx.x;
+            if (c < nv) dst[2 * nq + c] = silu_f(y[r]);
+        }
+    } else if (unit < qk_units + v_units + g_units) {
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int c = (unit - qk_units - v_units) * 1024 + r * 256 + threadIdx.x;
+            if (c < ng) {
+                const float z = p.a[(size_t)t * ng + c] + p.dt_bias[c];
+                const float sp = z > 20.f ? z : log1pf(expf(z));
+                p.g[(size_t)t * ng + c] = expf(-expf(p.a_log[c / d]) * sp);
+            }
+        }
+    } else {
+        for (int h = threadIdx.x; h < p.nh; h += blockDim.x) p.beta[(size_t)t * p.nh + h] = 1.0f / (1.0f + expf(-p.x[(size_t)t * p.ld + p.b_off + h]));
     }
-    for (int c = threadIdx.x; c < nv; c += blockDim.x) dst[2 * nq + c] = sm[2 * nq + c];
-    for (int c = threadIdx.x; c < p.nh * p.d; c += blockDim.x) {
-        const int h = c / p.d;
-        const float z = p.a[(size_t)t * p.nh * p.d + c] + p.dt_bias[c];
-        const float sp = z > 20.f ? z : log1pf(expf(z));
-        p.g[(size_t)t * p.nh * p.d + c] = expf(-expf(p.a_log[h]) * sp);
     }
-    for (int h = threadIdx.x; h < p.nh; h += blockDim.x) p.beta[(size_t)t * p.nh + h] = 1.0f / (1.0f + expf(-p.x[(size_t)t * p.ld + p.b_off + h]));
 }
 
 // The convolution's rows after the step: the raw projections of the sequence's last taps - 1 positions (zeros for
@@ -268,20 +345,17 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     if (!illm_delta_rule_supported(d, dv, taps) || nkv <= 0 || nh % nkv) return ILLM_ERR_BAD_ARG;
     const long long C = 2LL * nkv * d + (long long)nh * dv;
     if (state_elems < (long long)nh * d * dv + (taps - 1) * C) return ILLM_ERR_BAD_ARG;
-    if (C * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     DeltaArgs p;
-    p.x = x; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off;
+    p.x = x; p.T = T; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off; p.b_off = b_off;
     p.a = a; p.nh = nh; p.nkv = nkv; p.d = d; p.dv = dv; p.taps = taps;
     p.conv_q = conv_q; p.conv_k = conv_k; p.conv_v = conv_v; p.a_log = a_log; p.dt_bias = dt_bias; p.q_scale = q_scale;
     p.state = state; p.state_elems = state_elems; p.slots = slots; p.cu_q = cu_q; p.token_pos = token_pos; p.token_seq = token_seq;
     p.seq_lens = seq_lens; p.qkv = qkv; p.g = g; p.beta = beta; p.out = out;
-    static bool raised = false;
-    if (!raised) {
-        cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        raised = true;
-    }
-    illm_launch(delta_prep_kernel, dim3(T), dim3(256), (size_t)C * sizeof(float), s, p);
+    const int hpb = d > 256 ? 1 : 256 / ((d + 31) / 32 * 32);
+    const long long units = (2LL * nkv + hpb - 1) / hpb + ((long long)nh * dv + 1023) / 1024 + ((long long)nh * d + 1023) / 1024 + 1;
+    if (units > 65535) return ILLM_ERR_BAD_ARG;
+    illm_launch(delta_prep_kernel, dim3((T + DL_PREP_TOKENS - 1) / DL_PREP_TOKENS, (unsigned)units), dim3(256), 0, s, p);
     if (taps > 1) illm_launch(conv_state_kernel, dim3((unsigned)((C + 127) / 128), B), dim3(128), 0, s, p);
     if (d <= 32) launch_scan<1>(p, B, s);
     else if (d <= 64) launch_scan<2>(p, B, s);

@@ -117,12 +117,104 @@ head_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
     }
 }
 
+// The same maps for the few rows of a single-token step (bfloat16 matrices, at most 16 rows): a block per (head, 32
+// outputs), the rows' inputs in shared memory, the matrix read once, 16 bytes per thread where its rows are contiguous
+// in the inner index.  NN: 8 slices of the inner index per output, added in order through shared memory; NT: 8 lanes per
+// output, added by shuffles.
+#define HV_ROWS 16
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+head_gemv_nn_kernel(const TX* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int T, int N, int K) {
+    pdl_grid_sync();
+    extern __shared__ float hv_sm[];               // x [T, K], then the partial sums [8, T, 32]
+    const int h = blockIdx.y, H = gridDim.y, n = blockIdx.x * 32 + (threadIdx.x & 31), ks = threadIdx.x >> 5;
+    float* xs = hv_sm;
+    float* red = hv_sm + T * K;
+    for (int e = threadIdx.x; e < T * K; e += 256) xs[e] = to_f32(x[((size_t)(e / K) * H + h) * K + e % K]);
+    __syncthreads();
+    float acc[HV_ROWS];
+#pragma unroll
+    for (int t = 0; t < HV_ROWS; t++) acc[t] = 0.f;
+    if (n < N) {
+        const bf16* wp = w + (size_t)h * K * N + n;
+#pragma unroll 4
+        for (int k = ks; k < K; k += 8) {
+            const float wv = to_f32(wp[(size_t)k * N]);
+#pragma unroll
+            for (int t = 0; t < HV_ROWS; t++)
+                if (t < T) acc[t] = fmaf(xs[t * K + k], wv, acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < HV_ROWS; t++)
+        if (t < T) red[(ks * T + t) * 32 + (threadIdx.x & 31)] = acc[t];
+    __syncthreads();
+    for (int e = threadIdx.x; e < T * 32; e += 256) {
+        const int t = e >> 5, nl = e & 31, nn = blockIdx.x * 32 + nl;
+        if (nn >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) v += red[(q * T + t) * 32 + nl];
+        y[((size_t)t * H + h) * N + nn] = from_f32<TY>(v);
+    }
+}
+
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+head_gemv_nt_kernel(const TX* __restrict__ x, const bf16* __restrict__ w, TY* __restrict__ y, int T, int N, int K) {
+    pdl_grid_sync();
+    extern __shared__ float hv_sm[];               // x [T, K]
+    const int h = blockIdx.y, H = gridDim.y, n = blockIdx.x * 32 + (threadIdx.x >> 3), kl = threadIdx.x & 7;
+    for (int e = threadIdx.x; e < T * K; e += 256) hv_sm[e] = to_f32(x[((size_t)(e / K) * H + h) * K + e % K]);
+    __syncthreads();
+    float acc[HV_ROWS];
+#pragma unroll
+    for (int t = 0; t < HV_ROWS; t++) acc[t] = 0.f;
+    if (n < N) {
+        const bf16* wp = w + ((size_t)h * N + n) * K;
+        for (int k = kl * 8; k < K; k += 64) {
+            float wv[8];
+            load8(wp + k, wv);
+#pragma unroll
+            for (int t = 0; t < HV_ROWS; t++)
+                if (t < T) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[t] = fmaf(hv_sm[t * K + k + j], wv[j], acc[t]);
+                }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < HV_ROWS; t++)
+        if (t < T) {
+            float v = acc[t];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            if (kl == 0 && n < N) y[((size_t)t * H + h) * N + n] = from_f32<TY>(v);
+        }
+}
+
 // x [T, heads * K] -> y [T, heads * N]; w [heads * N, K] (nn = 0) or [heads * K, N] (nn = 1).  dtype codes for x, w, y.
 extern "C" int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int T, int heads, int N, int K,
                               int nn, void* stream) {
     if (T <= 0) return 0;
     if (heads <= 0 || heads > 65535 || N <= 0 || K <= 0) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t hv_smem = ((size_t)T * K + (nn ? (size_t)8 * T * 32 : 0)) * sizeof(float);
+    if (T <= HV_ROWS && w_dtype == ILLM_BF16 && y_dtype == ILLM_BF16 && hv_smem <= 48 * 1024 && (nn || ((K & 7) == 0 && !((uintptr_t)w & 15)))) {
+        dim3 grid((N + 31) / 32, heads);
+#define ILLM_HV(TX)                                                                                                              \
+    do {                                                                                                                         \
+        if (nn) illm_launch(head_gemv_nn_kernel<TX, bf16>, grid, dim3(256), hv_smem, s, (const TX*)x, (const bf16*)w, (bf16*)y, T, N, K); \
+        else illm_launch(head_gemv_nt_kernel<TX, bf16>, grid, dim3(256), hv_smem, s, (const TX*)x, (const bf16*)w, (bf16*)y, T, N, K);    \
+    } while (0)
+        if (x_dtype == ILLM_F32) ILLM_HV(float);
+        else if (x_dtype == ILLM_BF16) ILLM_HV(bf16);
+        else return ILLM_ERR_BAD_ARG;
+#undef ILLM_HV
+        return illm_launch_status();
+    }
     for (int t0 = 0; t0 < T; t0 += 65535 * HG_BM) {
         const int n = min(T - t0, 65535 * HG_BM);
         dim3 grid((N + HG_BN - 1) / HG_BN, (n + HG_BM - 1) / HG_BM, heads);
