@@ -26,7 +26,7 @@
 
 struct DeltaArgs {
     const float* x;                 // [T, ld] the packed float32 projection
-    int T, ld, q_off, k_off, v_off, b_off;
+    int T, prep_tokens, ld, q_off, k_off, v_off, b_off;
     const float* a;                 // [T, nh * d] decay projection (before the bias)
     int nh, nkv, d, dv, taps;
     const float *conv_q, *conv_k, *conv_v;      // [channels, taps]
@@ -83,10 +83,10 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
     __shared__ float scratch[32];
     __shared__ float warp_ss[8];
     const int unit = blockIdx.y;
-    // a block takes DL_PREP_TOKENS tokens in turn: the look-ups at the start of a token are a chain of dependent loads,
+    // in a long step a block takes DL_PREP_TOKENS tokens in turn (one in a short step): the look-ups at the start of a token are a chain of dependent loads,
     // which a block of one token would spend most of its life on
 #pragma unroll 1
-    for (int t = blockIdx.x * DL_PREP_TOKENS; t < min(p.T, (int)(blockIdx.x + 1) * DL_PREP_TOKENS); t++) {
+    for (int t = blockIdx.x * p.prep_tokens; t < min(p.T, (int)(blockIdx.x + 1) * p.prep_tokens); t++) {
     __syncthreads();
     const int seq = p.token_seq[t], pos = p.token_pos[t];
     const int i_step = t - p.cu_q[seq];            // the token's place among the step's tokens of its sequence
@@ -355,7 +355,8 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     const int hpb = d > 256 ? 1 : 256 / ((d + 31) / 32 * 32);
     const long long units = (2LL * nkv + hpb - 1) / hpb + ((long long)nh * dv + 1023) / 1024 + ((long long)nh * d + 1023) / 1024 + 1;
     if (units > 65535) return ILLM_ERR_BAD_ARG;
-    illm_launch(delta_prep_kernel, dim3((T + DL_PREP_TOKENS - 1) / DL_PREP_TOKENS, (unsigned)units), dim3(256), 0, s, p);
+    p.prep_tokens = T >= 512 ? DL_PREP_TOKENS : 1;
+    illm_launch(delta_prep_kernel, dim3((T + p.prep_tokens - 1) / p.prep_tokens, (unsigned)units), dim3(256), 0, s, p);
     if (taps > 1) illm_launch(conv_state_kernel, dim3((unsigned)((C + 127) / 128), B), dim3(128), 0, s, p);
     if (d <= 32) launch_scan<1>(p, B, s);
     else if (d <= 64) launch_scan<2>(p, B, s);
