@@ -43,41 +43,43 @@ struct DeltaArgs {
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 
-// The convolution of one channel at token t: the taps oldest first (one chain of fused multiply-adds, the same whether a
-// row comes from the step or from the state), all inputs loaded before the chain starts.
+// The convolution of one channel at token t: the taps oldest first, one chain of fused multiply-adds, the same whether a
+// row comes from the step or from the state.  KT > 0: the number of taps at compile time; a token that has all its
+// earlier rows in the step itself (every token of a prompt but the first few) reads them with fixed offsets.
+template <int KT>
 __device__ __forceinline__ float conv_channel(const DeltaArgs& p, int t, int i_step, int pos, int c, int col, const float* __restrict__ taps,
                                               const float* __restrict__ conv_state, int C) {
-    const int K = p.taps;
+    const int K = KT > 0 ? KT : p.taps;
+    const float* xc = p.x + (size_t)t * p.ld + col;
     float y = 0.f;
-    if (K <= 8) {
-        float in[8], w[8];
+    if (KT > 0 && i_step >= KT - 1) {
+        float in[KT > 0 ? KT : 1], w[KT > 0 ? KT : 1];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            in[j] = 0.f;
-            w[j] = 0.f;
-            if (j < K && pos - j >= 0) {
-                in[j] = j <= i_step ? __ldg(p.x + (size_t)(t - j) * p.ld + col) : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
-                w[j] = __ldg(taps + K - 1 - j);
-            }
+        for (int j = 0; j < KT; j++) {
+            in[j] = __ldg(xc - (ptrdiff_t)j * p.ld);
+            w[j] = __ldg(taps + KT - 1 - j);
         }
 #pragma unroll
-        for (int j = 7; j >= 0; j--)
-            if (j < K && pos - j >= 0) y = fmaf(w[j], in[j], y);
+        for (int j = KT - 1; j >= 0; j--) y = fmaf(w[j], in[j], y);
         return y;
     }
     for (int j = K - 1; j >= 0; j--) {
         if (pos - j < 0) continue;
-        const float in = j <= i_step ? p.x[(size_t)(t - j) * p.ld + col] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
+        const float in = j <= i_step ? xc[-(ptrdiff_t)j * p.ld] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];
         y = fmaf(taps[K - 1 - j], in, y);
     }
     return y;
 }
+
+// silu of a convolved projection: the fast exponential and division (these values may be rounded to bfloat16 anyway)
+__device__ __forceinline__ float silu_fast(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 // grid (tokens, units), 256 threads.  A unit is a group of query or key heads (convolution, silu, unit vectors; as many
 // heads as fit 256 threads, a head of more than 256 channels alone), a piece of 1024 value channels (convolution, silu),
 // a piece of 1024 decay channels, or the write strengths of all heads.
 __device__ __forceinline__ int delta_heads_per_block(int d) { return d > 256 ? 1 : 256 / ((d + 31) / 32 * 32); }
 
+template <int KT>
 __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
     pdl_grid_sync();
     __shared__ float scratch[32];
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
         const int hh = is_q ? head : head - p.nkv;
         float v = 0.f;
         if (live)
-            v = silu_f(conv_channel(p, t, i_step, pos, head * d + i, (is_q ? p.q_off : p.k_off) + hh * d + i,
+            v = silu_fast(conv_channel<KT>(p, t, i_step, pos, head * d + i, (is_q ? p.q_off : p.k_off) + hh * d + i,
                                     (is_q ? p.conv_q : p.conv_k) + ((size_t)hh * d + i) * K, conv_state, C));
         const float ws = warp_sum(v * v);
         if ((threadIdx.x & 31) == 0) warp_ss[threadIdx.x >> 5] = ws;
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
             const int i = threadIdx.x + r * 256;
             v[r] = 0.f;
             if (i < d) {
-                v[r] = silu_f(conv_channel(p, t, i_step, pos, c0 + i, col0 + i, taps + (size_t)i * K, conv_state, C));
+                v[r] = silu_fast(conv_channel<KT>(p, t, i_step, pos, c0 + i, col0 + i, taps + (size_t)i * K, conv_state, C));
                 ss = fmaf(v[r], v[r], ss);
             }
         }
@@ -141,12 +143,12 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaArgs p) {
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int c = (unit - qk_units) * 1024 + r * 256 + threadIdx.x;
-            y[r] = c < nv ? conv_channel(p, t, i_step, pos, 2 * nq + c, p.v_off + c, p.conv_v + (size_t)c * K, conv_state, C) : 0.f;
+            y[r] = c < nv ? conv_channel<KT>(p, t, i_step, pos, 2 * nq + c, p.v_off + c, p.conv_v + (size_t)c * K, conv_state, C) : 0.f;
         }
 #pragma unroll
         for (int r = 0; r < 4; r++) {
             const int c = (unit - qk_units) * 1024 + r * 256 + threadIdx.x;
-            if (c < nv) dst[2 * nq + c] = silu_f(y[r]);
+            if (c < nv) dst[2 * nq + c] = silu_fast(y[r]);
         }
     } else if (unit < qk_units + v_units + g_units) {
 #pragma unroll
@@ -356,7 +358,12 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     const long long units = (2LL * nkv + hpb - 1) / hpb + ((long long)nh * dv + 1023) / 1024 + ((long long)nh * d + 1023) / 1024 + 1;
     if (units > 65535) return ILLM_ERR_BAD_ARG;
     p.prep_tokens = T >= 512 ? DL_PREP_TOKENS : 1;
-    illm_launch(delta_prep_kernel, dim3((T + p.prep_tokens - 1) / p.prep_tokens, (unsigned)units), dim3(256), 0, s, p);
+    const dim3 pgrid((T + p.prep_tokens - 1) / p.prep_tokens, (unsigned)units);
+    if (taps == 1) illm_launch(delta_prep_kernel<1>, pgrid, dim3(256), 0, s, p);
+    else if (taps == 2) illm_launch(delta_prep_kernel<2>, pgrid, dim3(256), 0, s, p);
+    else if (taps == 3) illm_launch(delta_prep_kernel<3>, pgrid, dim3(256), 0, s, p);
+    else if (taps == 4) illm_launch(delta_prep_kernel<4>, pgrid, dim3(256), 0, s, p);
+    else illm_launch(delta_prep_kernel<0>, pgrid, dim3(256), 0, s, p);
     if (taps > 1) illm_launch(conv_state_kernel, dim3((unsigned)((C + 127) / 128), B), dim3(128), 0, s, p);
     if (d <= 32) launch_scan<1>(p, B, s);
     else if (d <= 64) launch_scan<2>(p, B, s);
