@@ -107,6 +107,11 @@ CONFIGS = {
     "wide128": pz.random_config((D, L), width=96, vocab=150, heads=2, kv_heads=2, dim=128, vdim=16, conv=2, a_rank=8, g_rank=8, att_heads=20,
                                 att_dim=16, att_vdim=8, q_rank=32, kv_rank=128, window=130, scale=0.9, experts=2, top=2, expert_ff=48, ff=80,
                                 mlps=["moe", "dense"]),
+    # sizes that are multiples of nothing much: low ranks of 3 and 5, a query latent of 12, a key/value latent of 40, every
+    # expert chosen, a loop over all layers
+    "odd": pz.random_config((D, L, D), width=56, vocab=75, heads=3, kv_heads=1, dim=20, vdim=12, conv=2, a_rank=3, g_rank=5, att_heads=7,
+                            att_dim=12, att_vdim=20, q_rank=12, kv_rank=40, window=33, scale=0.8, experts=4, top=4, expert_ff=12, ff=44,
+                            mlps=["moe", "dense", "moe"], loop=(0, 3, 2), bigram=(7, 3, 1)),
 }
 
 
@@ -350,3 +355,20 @@ def test_trace_replay_program(models, tmp_path):
     for n, ref in enumerate(want):
         got = np.fromfile(os.path.join(out, f"{n}.f32"), "<f4").reshape(ref.shape)
         assert_close(got, ref, "float32", f"step {n}")
+
+
+def test_command_line(models):
+    """bin/llama on a Vizosun folder: greedy tokens of two requests, float32."""
+    import subprocess
+    d, cfg, w = models["mixed"]
+    prompts = [prompt(cfg, n, 90 + n) for n in (7, 12)]
+    want = [pz.greedy_generate(cfg, w, p, 6) for p in prompts]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    args = [os.path.join(root, "bin", "llama"), "-m", d, "-d", "float32", "-c", "128", "-n", "6", "--temp", "0", "--top_k", "0",
+            "--top_p", "1", "--repeat_penalty", "1", "-s", "1"]
+    for p in prompts:
+        args += ["--prompt-ids", ",".join(map(str, p))]
+    r = subprocess.run(args, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    got = [[int(t) for t in ln.split(": ")[1].split(",")] for ln in r.stdout.splitlines() if ln.startswith("[")]
+    assert got == want
