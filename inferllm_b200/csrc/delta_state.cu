@@ -192,6 +192,13 @@ __global__ void conv_state_kernel(DeltaArgs p) {
 // the quads 4 (l + L r) .. + 3 for r = 0..7, so that its q, k and g come as 16-byte reads of shared memory that the
 // lanes of a column make side by side; rows beyond d are padding (k = q = 0, so their state stays 0).  The two dot
 // products run as four chains each.
+__device__ __forceinline__ void dl_cp16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void dl_cp4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
 template <int L>
 __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     pdl_grid_sync();
@@ -211,58 +218,80 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
         const int i = 4 * (l + L * (r >> 2)) + (r & 3);
         S[r] = (live && i < d) ? S_col[i] : 0.f;
     }
-    // a tile of tokens in shared memory: q, k, g [tile, DPAD] each, v [tile, COLS], beta [tile]
-    float* sq = sm;
-    float* sk = sq + DL_TILE * DPAD;
-    float* sg = sk + DL_TILE * DPAD;
-    float* sv = sg + DL_TILE * DPAD;
-    float* sb = sv + DL_TILE * COLS;
+    // Two buffers of a tile of tokens in shared memory: q, k, g [tile, DPAD] each, v [tile, COLS], beta [tile].  The next
+    // tile is on its way (cp.async) while this one is computed.  The padding rows beyond d are written once.
+    constexpr int BUF = DL_TILE * (3 * DPAD + COLS + 1);
     const int j0 = blockIdx.x * COLS;
     const float* __restrict__ qkv = p.qkv;
     const float* __restrict__ gg = p.g;
     float* __restrict__ out = p.out;
-    for (int t0 = 0; t0 < n; t0 += DL_TILE) {
+    if (d < DPAD)
+        for (int e = threadIdx.x; e < 2 * DL_TILE * (DPAD - d); e += DL_THREADS) {
+            const int bb = e / (DL_TILE * (DPAD - d)), r = e % (DL_TILE * (DPAD - d));
+            const int at = (r / (DPAD - d)) * DPAD + d + r % (DPAD - d);
+            sm[bb * BUF + at] = 0.f;
+            sm[bb * BUF + DL_TILE * DPAD + at] = 0.f;
+            sm[bb * BUF + 2 * DL_TILE * DPAD + at] = 1.f;
+        }
+    const bool wide = (d & 3) == 0 && (C & 3) == 0;          // rows of q, k and the decay start on 16-byte boundaries
+    auto stage = [&](int buf, int t0) {
+        float* sq = sm + buf * BUF;
+        float* sk = sq + DL_TILE * DPAD;
+        float* sg = sk + DL_TILE * DPAD;
+        float* sv = sg + DL_TILE * DPAD;
+        float* sb = sv + DL_TILE * COLS;
         const int nt = min(DL_TILE, n - t0);
-        __syncthreads();
-        // the loads of a group of pieces first, then their stores: the reads are in flight together
-        constexpr int PIECES = DL_TILE * DPAD / DL_THREADS, GROUP = PIECES < 8 ? PIECES : 8;
-#pragma unroll 1
-        for (int e0 = 0; e0 < PIECES; e0 += GROUP) {
-            float rq[GROUP], rk[GROUP], rg[GROUP];
-#pragma unroll
-            for (int u = 0; u < GROUP; u++) {
-                const int e = (e0 + u) * DL_THREADS + threadIdx.x;
-                const int tt = e / DPAD, i = e % DPAD;
+        if (wide) {
+            const int per_row = d >> 2;
+            for (int e = threadIdx.x; e < nt * per_row; e += DL_THREADS) {
+                const int tt = e / per_row, i = (e - tt * per_row) * 4;
                 const size_t t = (size_t)(first + t0 + tt);
-                const bool in = i < d && tt < nt;
-                rq[u] = in ? __ldg(qkv + t * C + (size_t)hk * d + i) : 0.f;
-                rk[u] = in ? __ldg(qkv + t * C + nq + (size_t)hk * d + i) : 0.f;
-                rg[u] = in ? __ldg(gg + t * p.nh * d + (size_t)h * d + i) : 1.f;
+                dl_cp16(sq + tt * DPAD + i, qkv + t * C + (size_t)hk * d + i);
+                dl_cp16(sk + tt * DPAD + i, qkv + t * C + nq + (size_t)hk * d + i);
+                dl_cp16(sg + tt * DPAD + i, gg + t * p.nh * d + (size_t)h * d + i);
             }
-#pragma unroll
-            for (int u = 0; u < GROUP; u++) {
-                const int e = (e0 + u) * DL_THREADS + threadIdx.x;
-                sq[e] = rq[u];
-                sk[e] = rk[u];
-                sg[e] = rg[u];
+        } else {
+            for (int e = threadIdx.x; e < nt * d; e += DL_THREADS) {
+                const int tt = e / d, i = e - tt * d;
+                const size_t t = (size_t)(first + t0 + tt);
+                dl_cp4(sq + tt * DPAD + i, qkv + t * C + (size_t)hk * d + i);
+                dl_cp4(sk + tt * DPAD + i, qkv + t * C + nq + (size_t)hk * d + i);
+                dl_cp4(sg + tt * DPAD + i, gg + t * p.nh * d + (size_t)h * d + i);
             }
         }
         for (int e = threadIdx.x; e < nt * COLS; e += DL_THREADS) {
             const int tt = e / COLS, c = e - tt * COLS;
-            sv[e] = j0 + c < dv ? __ldg(qkv + (size_t)(first + t0 + tt) * C + 2 * nq + (size_t)h * dv + j0 + c) : 0.f;
+            if (j0 + c < dv) dl_cp4(sv + e, qkv + (size_t)(first + t0 + tt) * C + 2 * nq + (size_t)h * dv + j0 + c);
         }
-        for (int e = threadIdx.x; e < nt; e += DL_THREADS) sb[e] = __ldg(p.beta + (size_t)(first + t0 + e) * p.nh + h);
+        for (int e = threadIdx.x; e < nt; e += DL_THREADS) dl_cp4(sb + e, p.beta + (size_t)(first + t0 + e) * p.nh + h);
+    };
+    if (n > 0) stage(0, 0);
+    asm volatile("cp.async.commit_group;\n" ::);
+    for (int t0 = 0, it = 0; t0 < n; t0 += DL_TILE, it++) {
+        const int nt = min(DL_TILE, n - t0);
+        if (t0 + DL_TILE < n) stage((it + 1) & 1, t0 + DL_TILE);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 1;\n" ::);
         __syncthreads();
+        const float* sq = sm + (it & 1) * BUF;
+        const float* sk = sq + DL_TILE * DPAD;
+        const float* sg = sk + DL_TILE * DPAD;
+        const float* sv = sg + DL_TILE * DPAD;
+        const float* sb = sv + DL_TILE * COLS;
         for (int tt = 0; tt < nt; tt++) {
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DPAD);
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DPAD);
             const float4* g4 = reinterpret_cast<const float4*>(sg + tt * DPAD);
-            float4 kk[DL_ROWS / 4];
+            float4 kk[DL_ROWS / 4], qq[DL_ROWS / 4];
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
             for (int r = 0; r < DL_ROWS / 4; r++) {
-                const float4 g = g4[l + L * r];
                 kk[r] = k4[l + L * r];
+                qq[r] = q4[l + L * r];           // read now, used after the first reduction
+            }
+#pragma unroll
+            for (int r = 0; r < DL_ROWS / 4; r++) {
+                const float4 g = g4[l + L * r];
                 S[4 * r] *= g.x;
                 S[4 * r + 1] *= g.y;
                 S[4 * r + 2] *= g.z;
@@ -279,7 +308,7 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
             a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
             for (int r = 0; r < DL_ROWS / 4; r++) {
-                const float4 q = q4[l + L * r];
+                const float4 q = qq[r];
                 S[4 * r] = fmaf(kk[r].x, u, S[4 * r]);
                 S[4 * r + 1] = fmaf(kk[r].y, u, S[4 * r + 1]);
                 S[4 * r + 2] = fmaf(kk[r].z, u, S[4 * r + 2]);
@@ -294,6 +323,7 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
             for (int o = L / 2; o > 0; o >>= 1) oacc += __shfl_xor_sync(0xffffffffu, oacc, o);
             if (live && l == 0) out[(size_t)(first + t0 + tt) * p.nh * dv + (size_t)h * dv + j] = oacc;
         }
+        __syncthreads();          // the tile after the next one goes into this buffer
     }
     if (live) {
 #pragma unroll
@@ -309,7 +339,7 @@ extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 
 template <int L>
 static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
     constexpr int COLS = DL_THREADS / L;
-    size_t smem = (size_t)(DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
+    size_t smem = (size_t)(2 * DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
     // The scan is bound by what an SM's shared memory delivers per clock, so its blocks must spread over the SMs.  Launched
     // behind kernels that still hold most SMs, a small grid would be packed onto the few SMs that are free first (measured: 32
     // blocks, 2.5 ms instead of 0.95 ms).  Asking for more shared memory than the tiles need caps the blocks per SM at what an
