@@ -199,11 +199,11 @@ __device__ __forceinline__ void dl_cp4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
 }
 
-template <int L>
+template <int L, int ROWS>
 __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     pdl_grid_sync();
     extern __shared__ __align__(16) float sm[];
-    constexpr int COLS = DL_THREADS / L, DPAD = DL_ROWS * L;
+    constexpr int COLS = DL_THREADS / L, DPAD = ROWS * L;
     const int b = blockIdx.z, h = blockIdx.y, hk = h / (p.nh / p.nkv);
     const int d = p.d, dv = p.dv;
     const int l = threadIdx.x % L, jc = threadIdx.x / L;
@@ -212,9 +212,9 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     const int first = p.cu_q[b], n = p.cu_q[b + 1] - first;
     const int nq = p.nkv * d, C = 2 * nq + p.nh * dv;
     float* S_col = p.state + (size_t)p.slots[b] * p.state_elems + ((size_t)h * dv + (live ? j : 0)) * d;
-    float S[DL_ROWS];
+    float S[ROWS];
 #pragma unroll
-    for (int r = 0; r < DL_ROWS; r++) {
+    for (int r = 0; r < ROWS; r++) {
         const int i = 4 * (l + L * (r >> 2)) + (r & 3);
         S[r] = (live && i < d) ? S_col[i] : 0.f;
     }
@@ -282,15 +282,15 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * DPAD);
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * DPAD);
             const float4* g4 = reinterpret_cast<const float4*>(sg + tt * DPAD);
-            float4 kk[DL_ROWS / 4], qq[DL_ROWS / 4];
+            float4 kk[ROWS / 4], qq[ROWS / 4];
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < DL_ROWS / 4; r++) {
+            for (int r = 0; r < ROWS / 4; r++) {
                 kk[r] = k4[l + L * r];
                 qq[r] = q4[l + L * r];           // read now, used after the first reduction
             }
 #pragma unroll
-            for (int r = 0; r < DL_ROWS / 4; r++) {
+            for (int r = 0; r < ROWS / 4; r++) {
                 const float4 g = g4[l + L * r];
                 S[4 * r] *= g.x;
                 S[4 * r + 1] *= g.y;
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
             const float u = sb[tt] * (sv[tt * COLS + jc] - acc);
             a0 = a1 = a2 = a3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < DL_ROWS / 4; r++) {
+            for (int r = 0; r < ROWS / 4; r++) {
                 const float4 q = qq[r];
                 S[4 * r] = fmaf(kk[r].x, u, S[4 * r]);
                 S[4 * r + 1] = fmaf(kk[r].y, u, S[4 * r + 1]);
@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
     }
     if (live) {
 #pragma unroll
-        for (int r = 0; r < DL_ROWS; r++) {
+        for (int r = 0; r < ROWS; r++) {
             const int i = 4 * (l + L * (r >> 2)) + (r & 3);
             if (i < d) S_col[i] = S[r];
         }
@@ -336,21 +336,14 @@ __global__ void __launch_bounds__(DL_THREADS) delta_scan_kernel(DeltaArgs p) {
 
 extern "C" int illm_delta_rule_supported(int d, int dv, int taps) { return d >= 1 && d <= 16 * DL_ROWS && dv >= 1 && taps >= 1 && taps <= 64; }
 
-template <int L>
-static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
+template <int L, int ROWS>
+static void launch_scan(const DeltaArgs& p, int B, int n_sms, cudaStream_t s) {
     constexpr int COLS = DL_THREADS / L;
-    size_t smem = (size_t)(2 * DL_TILE * (3 * DL_ROWS * L + COLS + 1)) * sizeof(float);
+    size_t smem = (size_t)(2 * DL_TILE * (3 * ROWS * L + COLS + 1)) * sizeof(float);
     // The scan is bound by what an SM's shared memory delivers per clock, so its blocks must spread over the SMs.  Launched
     // behind kernels that still hold most SMs, a small grid would be packed onto the few SMs that are free first (measured: 32
     // blocks, 2.5 ms instead of 0.95 ms).  Asking for more shared memory than the tiles need caps the blocks per SM at what an
     // even spread gives.
-    static int n_sms = 0;
-    if (!n_sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
-        if (n_sms <= 0) n_sms = 1;
-    }
     const long long blocks = (long long)((p.dv + COLS - 1) / COLS) * p.nh * B;
     const long long per_sm = (blocks + n_sms - 1) / n_sms;
     if (per_sm < 5) {
@@ -359,10 +352,30 @@ static void launch_scan(const DeltaArgs& p, int B, cudaStream_t s) {
     }
     static bool raised = false;
     if (!raised) {
-        cudaFuncSetAttribute(delta_scan_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(delta_scan_kernel<L, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         raised = true;
     }
-    illm_launch(delta_scan_kernel<L>, dim3((p.dv + COLS - 1) / COLS, p.nh, B), dim3(DL_THREADS), smem, s, p);
+    illm_launch(delta_scan_kernel<L, ROWS>, dim3((p.dv + COLS - 1) / COLS, p.nh, B), dim3(DL_THREADS), smem, s, p);
+}
+
+// A column's rows over L lanes of 32 rows each, or, while the grid of ONE sequence then still fits the SMs once, over 2 L
+// lanes of 16 rows or 4 L lanes of 8: a sequence's tokens are a chain, and fewer rows per thread shorten every link of it
+// (one prompt of 2,048 tokens, 8 heads of 128 x 128: 0.78 / 0.62 ms with 32 / 16 rows; with two blocks on an SM the
+// shorter rows gain nothing).  The choice does not depend on the batch, or a row's bits would.
+template <int L>
+static void launch_scan_for(const DeltaArgs& p, int B, cudaStream_t s) {
+    static int n_sms = 0;
+    if (!n_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (n_sms <= 0) n_sms = 1;
+    }
+    constexpr int L2 = 2 * L <= 32 ? 2 * L : L, L4 = 4 * L <= 32 ? 4 * L : L2;
+    auto blocks_of = [&](int lanes) { return (long long)((p.dv + DL_THREADS / lanes - 1) / (DL_THREADS / lanes)) * p.nh; };
+    if (L4 != L2 && blocks_of(L4) <= n_sms) launch_scan<L4, 8>(p, B, n_sms, s);
+    else if (L2 != L && blocks_of(L2) <= n_sms) launch_scan<L2, 16>(p, B, n_sms, s);
+    else launch_scan<L, 32>(p, B, n_sms, s);
 }
 
 // x: [T, ld] float32 with q at q_off (nkv * d columns), k at k_off, v at v_off (nh * dv), beta's logits at b_off (nh).
@@ -395,10 +408,10 @@ extern "C" int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_o
     else if (taps == 4) illm_launch(delta_prep_kernel<4>, pgrid, dim3(256), 0, s, p);
     else illm_launch(delta_prep_kernel<0>, pgrid, dim3(256), 0, s, p);
     if (taps > 1) illm_launch(conv_state_kernel, dim3((unsigned)((C + 127) / 128), B), dim3(128), 0, s, p);
-    if (d <= 32) launch_scan<1>(p, B, s);
-    else if (d <= 64) launch_scan<2>(p, B, s);
-    else if (d <= 128) launch_scan<4>(p, B, s);
-    else if (d <= 256) launch_scan<8>(p, B, s);
-    else launch_scan<16>(p, B, s);
+    if (d <= 32) launch_scan_for<1>(p, B, s);
+    else if (d <= 64) launch_scan_for<2>(p, B, s);
+    else if (d <= 128) launch_scan_for<4>(p, B, s);
+    else if (d <= 256) launch_scan_for<8>(p, B, s);
+    else launch_scan_for<16>(p, B, s);
     return illm_launch_status();
 }
