@@ -474,7 +474,7 @@ ILLM_API int illm_stream_add(void* s, const void* delta, int dtype) {
 ILLM_API int illm_stream_flush(void* s) {
     return guard([&] { ((ResidualStream*)s)->flush(); });
 }
-ILLM_API int illm_stream_has_pending(void* s) { return ((ResidualStream*)s)->has_pending ? 1 : 0; }
+ILLM_API int illm_stream_has_pending(void* s) { return ((ResidualStream*)s)->has_pending || ((ResidualStream*)s)->has_pending2 ? 1 : 0; }
 ILLM_API int illm_sandbox_norm_forward(void* sbp, void* p, void* stream, const int* rows, long long n_rows, void** out) {
     return guard([&] { *out = ((PartHandle*)p)->norm->forward(*(ResidualStream*)stream, rows, n_rows).p; });
 }

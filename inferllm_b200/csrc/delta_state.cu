@@ -63,6 +63,19 @@ __device__ __forceinline__ float conv_channel(const DeltaArgs& p, int t, int i_s
         for (int j = KT - 1; j >= 0; j--) y = fmaf(w[j], in[j], y);
         return y;
     }
+    if (KT > 0) {          // the first tokens of a step: rows from the state and from the step, all loads before the chain
+        float in[KT > 0 ? KT : 1], w[KT > 0 ? KT : 1];
+#pragma unroll
+        for (int j = 0; j < KT; j++) {
+            in[j] = 0.f;
+            w[j] = __ldg(taps + KT - 1 - j);
+            if (pos - j >= 0) in[j] = j <= i_step ? __ldg(xc - (ptrdiff_t)j * p.ld) : conv_state[(size_t)(KT - 1 - (j - i_step)) * C + c];
+        }
+#pragma unroll
+        for (int j = KT - 1; j >= 0; j--)
+            if (pos - j >= 0) y = fmaf(w[j], in[j], y);
+        return y;
+    }
     for (int j = K - 1; j >= 0; j--) {
         if (pos - j < 0) continue;
         const float in = j <= i_step ? xc[-(ptrdiff_t)j * p.ld] : conv_state[(size_t)(K - 1 - (j - i_step)) * C + c];

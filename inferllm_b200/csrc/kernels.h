@@ -64,6 +64,7 @@ int illm_moe_gemm_tc(const void* xs, const void* w, void* y, int P, int E, int N
 // stream_ops.cu
 int illm_gated_act(const void* gu, void* out, int act_dtype, int T, int I, int act, void* stream);
 int illm_take_columns(const float* x, int ld, int off, int n_cols, void* y, int act_dtype, int T, void* stream);
+int illm_add2_rmsnorm(float* resid, const float* d1, const float* d2, const float* w, void* y, int act_dtype, int T, int H, float eps, void* stream);
 int illm_join_rows(const float* a, const float* b, int H, void* y, int act_dtype, int T, void* stream);
 
 // embedding.cu

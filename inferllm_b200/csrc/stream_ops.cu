@@ -78,3 +78,70 @@ extern "C" int illm_join_rows(const float* a, const float* b, int H, void* y, in
     else return ILLM_ERR_BAD_ARG;
     return illm_launch_status();
 }
+
+// add2_rmsnorm: resid[t, :] += d1[t, :] (+ d2[t, :]), all float32, and y[t, :] = resid[t, :] / sqrt(mean(resid^2) + eps) * w
+// in the activation dtype: the two sublayer outputs of a parallel block folded into the next layer's norm.  A block
+// per row, the row kept in shared memory between the two passes; the sum is (x + d1) + d2, as two separate additions give.
+template <typename TY>
+__global__ void __launch_bounds__(1024)
+add2_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ d1, const float* __restrict__ d2, const float* __restrict__ w,
+                    TY* __restrict__ y, int H, float eps, int vec) {
+    pdl_grid_sync();
+    extern __shared__ __align__(16) float row_sm[];
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    if (vec) {          // rows of whole 16-byte pieces: a thread's loads are all in flight before its first store
+        const float4* r4 = reinterpret_cast<const float4*>(resid + base);
+        const float4* a4 = reinterpret_cast<const float4*>(d1 + base);
+        const float4* b4 = d2 ? reinterpret_cast<const float4*>(d2 + base) : nullptr;
+        for (int c = threadIdx.x; c < H / 4; c += blockDim.x) {
+            float4 v = r4[c];
+            const float4 a = a4[c];
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            if (b4) {
+                const float4 b = b4[c];
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            reinterpret_cast<float4*>(resid + base)[c] = v;
+            reinterpret_cast<float4*>(row_sm)[c] = v;
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float v = resid[base + c] + d1[base + c];
+            if (d2) v += d2[base + c];
+            resid[base + c] = v;
+            row_sm[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) y[base + c] = from_f32<TY>((row_sm[c] * inv) * w[c]);
+}
+
+extern "C" int illm_add2_rmsnorm(float* resid, const float* d1, const float* d2, const float* w, void* y, int act_dtype, int T, int H, float eps,
+                                 void* stream) {
+    if (T <= 0 || H <= 0) return 0;
+    if (!d1 || (size_t)H * sizeof(float) > 200 * 1024) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)H * sizeof(float);
+    static bool raised = false;
+    if (!raised) {
+        cudaFuncSetAttribute(add2_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(add2_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        raised = true;
+    }
+    const int vec = (H & 3) == 0 && !((uintptr_t)resid & 15) && !((uintptr_t)d1 & 15) && !((uintptr_t)d2 & 15) ? 1 : 0;
+    // a thread per 16-byte piece up to 1,024 threads (the block size depends on the width alone)
+    int threads = ((vec ? H / 4 : H) + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+    if (act_dtype == ILLM_BF16) illm_launch(add2_rmsnorm_kernel<bf16>, dim3(T), dim3(threads), smem, s, resid, d1, d2, w, (bf16*)y, H, eps, vec);
+    else if (act_dtype == ILLM_F32) illm_launch(add2_rmsnorm_kernel<float>, dim3(T), dim3(threads), smem, s, resid, d1, d2, w, (float*)y, H, eps, vec);
+    else return ILLM_ERR_BAD_ARG;
+    return illm_launch_status();
+}

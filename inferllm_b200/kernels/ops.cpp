@@ -646,6 +646,21 @@ Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& 
     return out;
 }
 
+Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& w, float eps, DType out_dtype) {
+    need(resid, "resid", true, DType::F32);
+    need(d1, "delta", true, DType::F32);
+    need(w, "norm weight", true, DType::F32);
+    if (d2) need(*d2, "second delta", true, DType::F32);
+    if (d1.rows != resid.rows || d1.cols != resid.cols || (d2 && (d2->rows != resid.rows || d2->cols != resid.cols)) || w.rows * w.cols != resid.cols)
+        throw KernelError("add2_rmsnorm: the additions and the weight must have the stream's shape");
+    if (resid.cols > kMaxNormWidth) throw KernelError("add2_rmsnorm: width " + std::to_string(resid.cols) + " exceeds what one block's shared memory holds");
+    Mat y = new_mat(dev, resid.rows, resid.cols, out_dtype);
+    check_kernel(illm_add2_rmsnorm((float*)resid.p, (const float*)d1.p, d2 ? (const float*)d2->p : nullptr, (const float*)w.p, y.p,
+                                   code_of(out_dtype, "add2_rmsnorm"), (int)resid.rows, (int)resid.cols, eps, dev.stream()),
+                 "add2_rmsnorm");
+    return y;
+}
+
 Mat take_columns(Device& dev, const Mat& x, long long off, long long n, DType dtype) {
     need(x, "x", true, DType::F32);
     if (off < 0 || n <= 0 || off + n > x.cols) throw KernelError("take_columns: the columns lie outside the matrix");

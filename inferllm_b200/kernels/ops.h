@@ -228,6 +228,8 @@ enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3 };
 int gate_act_from_name(const std::string& name);        // ConfigError-free: -1 for an unknown name
 // act(gate) * up of x . w^T for any GateAct (silu takes the fused kernels of linear_gated)
 Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act);
+// resid += d1 (+ d2), all float32 [T, H], and the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: one kernel
+Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& weight_f32, float eps, DType out_dtype);
 // columns [off, off + n) of a float32 matrix as a contiguous matrix of `dtype`
 Mat take_columns(Device& dev, const Mat& x_f32, long long off, long long n, DType dtype);
 // [a, b] row by row (two float32 matrices of equal shape) as a matrix of `dtype`

@@ -216,12 +216,23 @@ struct RMSNorm : Norm {
         }
     }
     Mat forward_into_stream(ResidualStream& stream) override {
+        if (stream.has_pending2) stream.flush();
         if (weight.m.dtype != DType::F32) throw EngineError("rmsnorm: the norm after the sum needs its weight in float32 (float32_weight)");
         const MatOrPartials* d = stream.has_pending ? &stream.pending : nullptr;      // unreduced slices are added up by the kernel
         stream.has_pending = false;
         return ops::scale_add_rmsnorm(*rt->dev, stream.x, d, weight.m, residual_scale, eps, rt->dtype);
     }
     Mat forward(ResidualStream& stream, const int* rows, long long n_rows) override {
+        // float32 additions (one or two finished matrices) fold into one kernel with the norm; what that kernel does not
+        // take (a second addition otherwise, a float32 addition beside a 16-bit output, gathered rows) is added first
+        const bool f32_pending = stream.has_pending && !stream.pending.is_partials() && stream.pending.m.dtype == DType::F32;
+        if (f32_pending && rows == nullptr && weight.m.dtype == DType::F32 &&
+            (!stream.has_pending2 || (!stream.pending2.is_partials() && stream.pending2.m.dtype == DType::F32))) {
+            Mat y = ops::add2_rmsnorm(*rt->dev, stream.x, stream.pending.m, stream.has_pending2 ? &stream.pending2.m : nullptr, weight.m, eps, rt->dtype);
+            stream.has_pending = stream.has_pending2 = false;
+            return y;
+        }
+        if (stream.has_pending2 || (f32_pending && rt->dtype != DType::F32)) stream.flush();
         Mat y = ops::add_rmsnorm(*rt->dev, stream.x, stream.has_pending ? &stream.pending : nullptr, weight.m, eps, rt->dtype, rows, n_rows,
                                  rows == nullptr);
         if (rows == nullptr) stream.has_pending = false;
@@ -700,15 +711,14 @@ struct PostNormBlock : Block {
 
 // "parallel": one norm, and both sublayers read its output:
 //     h = norm1(x);  x = x + mixer(h) + ffn(h)
-// (a layer without a feed-forward adds the mixer alone).  The sublayers' outputs are added to the float32 stream one
-// after the other, unrounded if they come in float32.
+// (a layer without a feed-forward adds the mixer alone).  The sublayers' outputs stay pending in the stream, and the next
+// layer's norm adds them, the mixer's first, to the float32 stream in the kernel that norms it, unrounded if they come in
+// float32.
 struct ParallelBlock : Block {
     void forward(ResidualStream& stream, const StepContext& ctx, const CacheView& cache, bool writes) override {
-        stream.flush();
-        Mat h = norms.at("norm1")->forward(stream, nullptr, 0);
+        Mat h = norms.at("norm1")->forward(stream, nullptr, 0);       // folds in what the layer before left pending
         stream.add(mixer->forward(h, ctx, cache, writes, false));
-        if (ffn) stream.add(ffn->forward(h, ctx, false));
-        stream.flush();
+        if (ffn) stream.add_second(ffn->forward(h, ctx, false));
     }
 };
 

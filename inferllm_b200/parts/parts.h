@@ -124,25 +124,34 @@ struct CacheView {
     StateView st;
 };
 
-// The float32 residual stream [T, H] with at most one addition pending.  A part's output is not added
-// at once: the next norm adds it while it reads the row anyway (one kernel for add + norm), which is
+// The float32 residual stream [T, H] with an addition pending (or two: the sublayers of a parallel block).  A part's
+// output is not added at once: the next norm adds it while it reads the row anyway (one kernel for add + norm), which is
 // also where the sum is rounded: never, it stays float32.
 struct ResidualStream {
     Device* dev = nullptr;
     Mat x;
-    bool has_pending = false;
-    MatOrPartials pending;
+    bool has_pending = false, has_pending2 = false;
+    MatOrPartials pending, pending2;
     Mat h;      // the stream's rows in the compute dtype, where a block keeps them (norm after the sum); empty otherwise
     void add(const MatOrPartials& delta) {
-        if (has_pending) flush();
+        if (has_pending || has_pending2) flush();
         pending = delta;
         has_pending = true;
     }
-    Mat& flush() {
-        if (has_pending) {
-            ops::residual_add(*dev, x, pending);
-            has_pending = false;
+    // A second addition behind a pending one, both finished matrices: x + pending + delta, added in that order by flush()
+    // or by a norm that folds both in.  Anything else is added like add().
+    void add_second(const MatOrPartials& delta) {
+        if (has_pending && !has_pending2 && !pending.is_partials() && !delta.is_partials()) {
+            pending2 = delta;
+            has_pending2 = true;
+        } else {
+            add(delta);
         }
+    }
+    Mat& flush() {
+        if (has_pending) ops::residual_add(*dev, x, pending);
+        if (has_pending2) ops::residual_add(*dev, x, pending2);
+        has_pending = has_pending2 = false;
         return x;
     }
 };
