@@ -26,10 +26,16 @@
 // goes on, so a fault in the pipeline ends the kernel instead of hanging the GPU.
 #include "tc_common.cuh"
 
+template <int ACT> __device__ __forceinline__ float tc_gate_act(float g) {
+    if (ACT == 2) return fmaxf(g, 0.f);
+    if (ACT == 3) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + __expf(-g));
+}
+
 // D[ra, rb] = sum_k A[ra, k] B[rb, k];  SWAP = false: C[ra * ldc + rb];  SWAP = true: C[rb * ldc + ra].
 #define TC_MAX_STAGES 12
 
-template <int BN, bool SWAP, typename TOut, bool GATED = false>
+template <int BN, bool SWAP, typename TOut, int GATED = 0>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TOut* __restrict__ C, long long split_stride, int ldc, int RA, int RB, int k_iters_total,
@@ -139,13 +145,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tmem_ld16(tmem + ((unsigned)(quad * 32) << 16) + (unsigned)c0, v);
                 if (SWAP && GATED) {
                     // weight rows 2i, 2i + 1 are gate and up of output i: neighbouring lanes hold them,
-                    // the even lane writes silu(gate) * up (ldc = outputs per token)
+                    // the even lane writes act(gate) * up (ldc = outputs per token; GATED 1 silu, 2 relu, 3 tanh-form gelu)
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
                         const int rb = rb0 + c0 + j;
                         if (!(lane & 1) && rb < RB && ra + 1 < RA)
-                            store_out<TOut>(Cz + (size_t)rb * ldc + (ra >> 1), (v[j] / (1.0f + __expf(-v[j]))) * up);
+                            store_out<TOut>(Cz + (size_t)rb * ldc + (ra >> 1), tc_gate_act<GATED>(v[j]) * up);
                     }
                 } else if (SWAP) {
 #pragma unroll
@@ -234,7 +240,7 @@ static int pick_stages(int stage_bytes, long long n_blocks, int k_iters_per_bloc
     return stages < 2 ? 2 : stages;
 }
 
-template <int BN, bool SWAP, typename TOut, bool GATED = false>
+template <int BN, bool SWAP, typename TOut, int GATED = 0>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TOut* C, long long split_stride, int ldc,
                      int RA, int RB, int k_iters, int splits, int* err, cudaStream_t s) {
     const int stage_bytes = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
@@ -309,12 +315,12 @@ extern "C" int illm_gemm_bf16_tc(const void* X, const void* W, void* out, int ou
 }
 
 // Decode-sized product (M <= 64) of a gated feed-forward's packed weight, whose rows are gate and up
-// of an output in turn: out[M, N / 2] = silu(gate) * up in bfloat16, straight from the accumulator
+// of an output in turn: out[M, N / 2] = act(gate) * up (act 1 silu, 2 relu, 3 tanh-form gelu) in bfloat16, straight from the accumulator
 // (formula src/kern/naive/naive.cpp:80-89), without splitting K.
-extern "C" int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int* err,
+extern "C" int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int act, int* err,
                                        void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64 || (N & 1) || K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ILLM_ERR_BAD_ARG;
+    if (M > 64 || (N & 1) || K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15) || act < 1 || act > 3) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
     CUtensorMap ma, mb;
@@ -323,9 +329,16 @@ extern "C" int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, 
     if ((rc = make_map(&ma, W, N, K, TC_BM)) != 0) return rc;
     if ((rc = make_map(&mb, X, M, K, bn)) != 0) return rc;
     bf16* o = (bf16*)out;
-    if (bn == 16) return launch_tc<16, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
-    if (bn == 32) return launch_tc<32, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
-    return launch_tc<64, true, bf16, true>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);
+#define ILLM_TCG(ACT)                                                                                                \
+    do {                                                                                                             \
+        if (bn == 16) return launch_tc<16, true, bf16, ACT>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);           \
+        if (bn == 32) return launch_tc<32, true, bf16, ACT>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);           \
+        return launch_tc<64, true, bf16, ACT>(ma, mb, o, 0, N / 2, N, M, k_iters, 1, err, s);                         \
+    } while (0)
+    if (act == 2) ILLM_TCG(2);
+    if (act == 3) ILLM_TCG(3);
+    ILLM_TCG(1);
+#undef ILLM_TCG
 }
 
 // out[i] = sum over slices (ascending) of ws[z][i]: the stand-alone form of the reduction.

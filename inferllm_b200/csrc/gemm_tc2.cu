@@ -69,6 +69,13 @@ __device__ __forceinline__ void umma_commit_pair(unsigned bar) {
         ::"r"(bar), "h"((unsigned short)3) : "memory");
 }
 
+// the activation of a gated epilogue: EPI 1 silu, 2 relu, 3 tanh-form gelu
+template <int EPI> __device__ __forceinline__ float t2_gate_act(float g) {
+    if (EPI == 2) return fmaxf(g, 0.f);
+    if (EPI == 3) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    return g / (1.0f + __expf(-g));
+}
+
 template <int EPI, typename TOut>
 __global__ void __launch_bounds__(T2_THREADS)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -179,7 +186,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (!alive) break;
             tc_fence_after();
             const unsigned tbase = tmem + ((unsigned)(quad * 32) << 16) + (unsigned)(buf * T2_BN);
-            if (EPI == 1) {
+            if (EPI >= 1) {
                 // columns 2i, 2i + 1 of the product are gate and up of output i (ldc = outputs per row)
 #pragma unroll 1
                 for (int c0 = 0; c0 < T2_BN; c0 += 16) {
@@ -187,7 +194,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     float v[16], r[8];
                     tmem_ld16(tbase + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) r[j] = (v[2 * j] / (1.0f + __expf(-v[2 * j]))) * v[2 * j + 1];
+                    for (int j = 0; j < 8; j++) r[j] = t2_gate_act<EPI>(v[2 * j]) * v[2 * j + 1];
                     if (ra < RA) {
                         const int o0 = (rb0 + c0) / 2;
                         TOut* dst = C + (size_t)ra * ldc + o0;
@@ -295,16 +302,18 @@ static int t2_launch(const void* X, const void* W, TOut* out, int ldc, int M, in
     return illm_launch_status();
 }
 
-// C = X . W^T (epi 0, C [M, N]) or the gated activation of it (epi 1, C [M, N / 2], W's rows gate
-// and up of an output in turn).  X, W 16-byte aligned; K % 8 == 0.
+// C = X . W^T (epi 0, C [M, N]) or the gated activation of it (epi 1 silu, 2 relu, 3 tanh-form gelu: C [M, N / 2], W's
+// rows gate and up of an output in turn).  X, W 16-byte aligned; K % 8 == 0.
 extern "C" int illm_gemm_bf16_tc2(const void* X, const void* W, void* out, int out_dtype, int epi, int M, int N,
                                   int K, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return ILLM_ERR_BAD_ARG;
-    if (epi == 1 && (N & 1)) return ILLM_ERR_BAD_ARG;
+    if (epi >= 1 && (N & 1)) return ILLM_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (epi == 0 && out_dtype == ILLM_BF16) return t2_launch<0, bf16>(X, W, (bf16*)out, N, M, N, K, err, s);
     if (epi == 0 && out_dtype == ILLM_F32) return t2_launch<0, float>(X, W, (float*)out, N, M, N, K, err, s);
     if (epi == 1 && out_dtype == ILLM_BF16) return t2_launch<1, bf16>(X, W, (bf16*)out, N / 2, M, N, K, err, s);
+    if (epi == 2 && out_dtype == ILLM_BF16) return t2_launch<2, bf16>(X, W, (bf16*)out, N / 2, M, N, K, err, s);
+    if (epi == 3 && out_dtype == ILLM_BF16) return t2_launch<3, bf16>(X, W, (bf16*)out, N / 2, M, N, K, err, s);
     return ILLM_ERR_BAD_ARG;
 }

@@ -78,7 +78,7 @@ int illm_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int
 // gemm_tc.cu
 int illm_gemm_bf16_tc_tune(int stages);
 int illm_gemm_bf16_tc(const void* X, const void* W, void* out, int out_dtype, int M, int N, int K, float* ws, int splits, int* err, void* stream, int skip_reduce);
-int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int* err, void* stream);
+int illm_gemm_bf16_tc_gated(const void* X, const void* W, void* out, int M, int N, int K, int act, int* err, void* stream);
 int illm_splitk_reduce(const float* ws, void* out, int out_dtype, long long n, int splits, void* stream);
 
 // gemm_tc2.cu

@@ -269,11 +269,11 @@ MatOrPartials gemm_bf16_tc(Device& dev, const Mat& x, const Mat& w, DType out_dt
     return r;
 }
 
-Mat gemm_bf16_tc2(Device& dev, const Mat& x, const Mat& w, DType out_dtype, bool gated) {
+Mat gemm_bf16_tc2(Device& dev, const Mat& x, const Mat& w, DType out_dtype, bool gated, int act) {
     check_product(x, w, "gemm_bf16_tc2", gated);
     const long long M = x.rows, K = x.cols, N = w.rows;
     Mat out = new_mat(dev, M, gated ? N / 2 : N, out_dtype);
-    check_kernel(illm_gemm_bf16_tc2(x.p, w.p, out.p, code_of(out_dtype, "gemm_bf16_tc2"), gated ? 1 : 0, (int)M, (int)N, (int)K,
+    check_kernel(illm_gemm_bf16_tc2(x.p, w.p, out.p, code_of(out_dtype, "gemm_bf16_tc2"), gated ? act : 0, (int)M, (int)N, (int)K,
                                     dev.tc_error_word(), dev.stream()),
                  "gemm_bf16_tc2");
     return out;
@@ -308,7 +308,8 @@ MatOrPartials linear(Device& dev, GemmBackend backend, const Mat& x, const Mat& 
     return r;
 }
 
-Mat linear_gated(Device& dev, GemmBackend backend, const Mat& x, const Mat& w) {
+Mat linear_gated(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act) {
+    if (act < kActSilu || act > kActGeluTanh) throw KernelError("linear_gated: unknown activation");
     const long long M = x.rows, K = x.cols, N = w.rows;
     if (x.dtype == DType::BF16 && w.dtype == DType::BF16 && M > 0 && K % 8 == 0 && N % 2 == 0 && !((uintptr_t)x.p & 15) &&
         !((uintptr_t)w.p & 15)) {
@@ -316,14 +317,19 @@ Mat linear_gated(Device& dev, GemmBackend backend, const Mat& x, const Mat& w) {
         if (tc && M <= 64 && gemm_tc_splits(M, N, K, dev.n_sms()) == 1) {
             check_product(x, w, "gemm_bf16_tc_gated", true);
             Mat out = new_mat_exact(dev, M, N / 2, DType::BF16);
-            check_kernel(illm_gemm_bf16_tc_gated(x.p, w.p, out.p, (int)M, (int)N, (int)K, dev.tc_error_word(), dev.stream()),
+            check_kernel(illm_gemm_bf16_tc_gated(x.p, w.p, out.p, (int)M, (int)N, (int)K, act, dev.tc_error_word(), dev.stream()),
                          "gemm_bf16_tc_gated");
             return out;
         }
         if (N >= 256 && ((backend == GemmBackend::TC && M > 128) || (backend == GemmBackend::Auto && M >= kGatedPromptsOnTcMinTokens)))
-            return gemm_bf16_tc2(dev, x, w, DType::BF16, true);
+            return gemm_bf16_tc2(dev, x, w, DType::BF16, true, act);
     }
-    return swiglu(dev, linear(dev, backend, x, w, x.dtype, true));
+    if (act == kActSilu) return swiglu(dev, linear(dev, backend, x, w, x.dtype, true));
+    Mat gu = linear(dev, backend, x, w, x.dtype, false).m;
+    if (gu.cols % 2) throw KernelError("gated activation: the packed projection must have an even number of columns");
+    Mat out = new_mat(dev, gu.rows, gu.cols / 2, gu.dtype);
+    check_kernel(illm_gated_act(gu.p, out.p, code_of(gu.dtype, "gated_act"), (int)gu.rows, (int)(gu.cols / 2), act, dev.stream()), "gated_act");
+    return out;
 }
 
 // ---- rotation and attention
@@ -635,15 +641,6 @@ int gate_act_from_name(const std::string& name) {
     if (name == "relu") return kActRelu;
     if (name == "gelu_tanh") return kActGeluTanh;
     return -1;
-}
-
-Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act) {
-    if (act == kActSilu) return linear_gated(dev, backend, x, w);
-    Mat gu = linear(dev, backend, x, w, x.dtype, false).m;
-    if (gu.cols % 2) throw KernelError("gated activation: the packed projection must have an even number of columns");
-    Mat out = new_mat(dev, gu.rows, gu.cols / 2, gu.dtype);
-    check_kernel(illm_gated_act(gu.p, out.p, code_of(gu.dtype, "gated_act"), (int)gu.rows, (int)(gu.cols / 2), act, dev.stream()), "gated_act");
-    return out;
 }
 
 Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& w, float eps, DType out_dtype) {

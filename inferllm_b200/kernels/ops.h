@@ -128,12 +128,13 @@ Mat materialize(Device& dev, const Partials& p, DType dtype);
 Mat swiglu(Device& dev, const MatOrPartials& gu);
 Mat gemm_f32(Device& dev, const Mat& x, const Mat& w);
 MatOrPartials gemm_bf16_tc(Device& dev, const Mat& x, const Mat& w, DType out_dtype, int splits /* 0: by policy */, bool defer_reduce);
-Mat gemm_bf16_tc2(Device& dev, const Mat& x, const Mat& w, DType out_dtype, bool gated);
+Mat gemm_bf16_tc2(Device& dev, const Mat& x, const Mat& w, DType out_dtype, bool gated, int act = 1 /* kActSilu */);
 // x [M, K] . w [N, K]^T.  defer_reduce allows the result to come back as unreduced slices (only a
 // caller that hands it to add_rmsnorm, the rotation or the fused decode attention asks).
 MatOrPartials linear(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, DType out_dtype, bool defer_reduce);
-// silu(gate) * up of x . w^T, where w's rows 2i, 2i + 1 are the gate and the up row of output i.
-Mat linear_gated(Device& dev, GemmBackend backend, const Mat& x, const Mat& w);
+// act(gate) * up of x . w^T, where w's rows 2i, 2i + 1 are the gate and the up row of output i (act: a GateAct, silu
+// by default); the product kernels of the package apply it in their epilogues.
+Mat linear_gated(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act = 1 /* kActSilu */);
 
 struct Geometry { int n_heads, n_kv_heads, head_dim; };
 // Rotate Q (and K) of the packed projection and store K, V in the cache pages.  cos_sin: float32
@@ -226,8 +227,6 @@ Mat group_norm_gate(Device& dev, const Mat& o_f32, int group, const float* w, fl
 // Activations of the gated feed-forward: act(gate) * up.
 enum GateAct { kActSilu = 1, kActRelu = 2, kActGeluTanh = 3 };
 int gate_act_from_name(const std::string& name);        // ConfigError-free: -1 for an unknown name
-// act(gate) * up of x . w^T for any GateAct (silu takes the fused kernels of linear_gated)
-Mat linear_gated_act(Device& dev, GemmBackend backend, const Mat& x, const Mat& w, int act);
 // resid += d1 (+ d2), all float32 [T, H], and the RMS norm of the new rows times w (float32 [H]) in `out_dtype`: one kernel
 Mat add2_rmsnorm(Device& dev, const Mat& resid, const Mat& d1, const Mat* d2, const Mat& weight_f32, float eps, DType out_dtype);
 // columns [off, off + n) of a float32 matrix as a contiguous matrix of `dtype`

@@ -57,7 +57,7 @@ _KERNEL_SIGNATURES = {
     "illm_rope_kv_write_partials": [P_, P_, I_, LL_, P_, P_, P_, P_, I_, P_, P_, I_, I_, I_, I_, I_, I_, I_, I_, I_, P_, P_],
     "illm_gemm_bf16_tc2": [P_, P_, P_, I_, I_, I_, I_, I_, P_, P_],
     "illm_swiglu_partials": [P_, I_, LL_, P_, I_, I_, P_],
-    "illm_gemm_bf16_tc_gated": [P_, P_, P_, I_, I_, I_, P_, P_],
+    "illm_gemm_bf16_tc_gated": [P_, P_, P_, I_, I_, I_, I_, P_, P_],
     "illm_attention_prefill_tc": [P_, I_, I_, P_, P_, LL_, P_, I_, P_, P_, P_, I_, I_, I_, I_, I_, I_, I_, F_, P_, P_],
     "illm_gemm_f32_nt": [P_, P_, P_, I_, I_, I_, I_, I_, I_, P_, P_],
     "illm_argmax": [P_, I_, I_, I_, P_, P_, P_, P_],
@@ -670,7 +670,7 @@ def gemm_bf16_tc_gated(x, w):
         raise KernelError(f"gemm_bf16_tc_gated: x {tuple(x.shape)}, w {tuple(w.shape)}: at most 64 rows, K a multiple of 8, "
                           "an even number of weight rows")
     out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-    _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K, _ptr(tc_error_word(x.device)), _stream()),
+    _check(load().illm_gemm_bf16_tc_gated(_ptr(x), _ptr(w), _ptr(out), M, N, K, 1, _ptr(tc_error_word(x.device)), _stream()),
            "gemm_bf16_tc_gated")
     return out
 

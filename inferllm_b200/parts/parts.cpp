@@ -524,7 +524,7 @@ struct Attention : Mixer {
 // one product feeds the activation, and where the package's own kernels run that product the
 // activation is their epilogue (ops::linear_gated).
 // `names` renames the three tensors; `output_dtype` = "float32" leaves the down projection unrounded;
-// `activation` is "silu" (default), "relu" or "gelu_tanh" (the latter two run the product and a kernel of their own).
+// `activation` is "silu" (default), "relu" or "gelu_tanh" (each the epilogue of the package's own product kernels).
 struct GatedMLP : FeedForward {
     long long hidden, inter;
     bool out_f32;
@@ -560,7 +560,7 @@ struct GatedMLP : FeedForward {
     }
     MatOrPartials forward(const Mat& h, const StepContext&, bool may_defer) override {
         Device& dev = *rt->dev;
-        return ops::linear(dev, rt->gemm, ops::linear_gated_act(dev, rt->gemm, h, w_gate_up, act), w_down, out_f32 ? DType::F32 : rt->dtype,
+        return ops::linear(dev, rt->gemm, ops::linear_gated(dev, rt->gemm, h, w_gate_up, act), w_down, out_f32 ? DType::F32 : rt->dtype,
                            may_defer);
     }
 };

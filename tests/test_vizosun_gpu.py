@@ -155,6 +155,21 @@ def test_mechanism_alone(tmp_path, name, dtype):
     assert_close(in_portions(eng, ids, [1]), ref, dtype, name + " token by token")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_through_the_fused_products(tmp_path, dtype):
+    """A prompt long enough, and a feed-forward wide enough, for the product kernels whose epilogue is the gate's
+    activation (relu here), and for the experts' products on row tiles of 128."""
+    cfg = pz.random_config((L, L), mlps=["dense", "moe"], bigram=None, width=64, ff=256, expert_ff=64, experts=4, top=2, window=50,
+                           att_heads=2, att_dim=16, att_vdim=16, q_rank=16, kv_rank=64)
+    w = write_model(str(tmp_path), cfg, 21)
+    ids = prompt(cfg, 600, 8)
+    ref = pz.forward(cfg, w, ids)
+    eng = engine(str(tmp_path), dtype, max_tokens=2048)
+    got = whole(eng, ids)
+    close(got, ref, dtype, "600 tokens in one step")
+    same_or_close(in_portions(eng, ids, [520, 1]), got, dtype, "the same, its last tokens one by one")
+
+
 # ------------------------------------------------------------------ whole models
 
 
