@@ -273,6 +273,9 @@ void write_random_model(const ArchConfig& config, const std::string& folder, uns
         f << cfg.dump(1) << "\n";
     }
     std::vector<TensorToWrite> tensors;
+    for (auto& d : decls)
+        for (long long n : d.second.shape)
+            if (n < 0) throw WeightError(d.first + ": a size that the configuration leaves to the weight file must be named for a random model");
     for (auto& d : decls) tensors.push_back(TensorToWrite{d.first, d.second.init == "int" ? DType::I32 : dtype, d.second.shape});
     Json meta = Json::object();
     meta.set("format", "pt");

@@ -190,3 +190,14 @@ def test_loop_runs_layers_in_passes():
     assert pz.layer_runs(cfg) == [(0, False), (1, True), (2, False), (1, True), (2, False)]
     cfg = pz.random_config((D, L, D), loop=(0, 1, 3))
     assert pz.layer_runs(cfg) == [(0, True), (0, True), (0, True), (1, False), (2, False)]
+
+
+def test_a_random_model_needs_the_ranks_named(tmp_path):
+    from inferllm_b200 import write_random_model
+    from inferllm_b200.binding import WeightError
+    cfg = pz.random_config((D,))
+    write_random_model(config_from_dict(cfg), str(tmp_path / "named"), 1)
+    del cfg["layers"][0]["mixer"]["a_rank"]
+    with pytest.raises(WeightError) as e:
+        write_random_model(config_from_dict(cfg), str(tmp_path / "open"), 1)
+    assert "a1" in str(e.value)
