@@ -48,6 +48,7 @@ int illm_delta_rule(const float* x, int T, int ld, int q_off, int k_off, int v_o
 
 // latent_attention.cu
 int illm_latent_prep(const float* x, int ld, int Q, int R, const float* wq, const float* wkv, float eps, const int* token_pos, const int* token_seq, const int* block_table, int max_pages, int page_size, void* cq_out, void* kc, int act_dtype, int T, int* err, void* stream);
+int illm_latent_attention_any(const void* q, const void* kc, const int* block_table, int max_pages, const int* token_pos, const int* token_seq, void* out, int act_dtype, int T, int H, int R, int page_size, int window, float scale, void* stream);
 int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, int T, int heads, int N, int K, int nn, void* stream);
 
 // moe.cu

@@ -233,3 +233,98 @@ extern "C" int illm_head_gemm(const void* x, int x_dtype, const void* w, int w_d
     }
     return illm_launch_status();
 }
+
+// Attention of every token over ONE shared key/value head of any width (the cached latent is key and value): the form
+// for widths that the framework's attention kernels do not take (not a multiple of 8, or beyond 256 channels).  A block
+// per (token, head), four warps that take the visible keys in turn (key j by warp (j - lo) mod 4, which depends on the
+// token's position alone), a lane holding every 32nd channel; float32 scores, an online softmax per warp, and the four
+// warps merged in a fixed order.  Positions p - window + 1 .. p are visible (window 0: all up to p).
+template <typename TA, int NR>
+__global__ void __launch_bounds__(128)
+latent_attention_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc, const int* __restrict__ block_table, int max_pages,
+                            const int* __restrict__ token_pos, const int* __restrict__ token_seq, TA* __restrict__ out, int H, int R,
+                            int page_size, int window, float scale) {
+    pdl_grid_sync();
+    extern __shared__ float la_sm[];               // per warp: R partial outputs, then the warps' (max, sum)
+    const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = token_pos[t];
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int* table = block_table + (size_t)token_seq[t] * max_pages;
+    float qv[NR], acc[NR];
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+        const int r = lane + 32 * i;
+        qv[i] = r < R ? to_f32(q[((size_t)t * H + h) * R + r]) * scale : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = lo + warp; j <= p; j += 4) {
+        const int page = table[j / page_size];
+        const TA* c = kc + ((size_t)page * page_size + j % page_size) * R;
+        float cv[NR], dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < NR; i++) {
+            const int r = lane + 32 * i;
+            cv[i] = (page >= 0 && r < R) ? to_f32(c[r]) : 0.f;
+            dot = fmaf(qv[i], cv[i], dot);
+        }
+        dot = warp_sum(dot);
+        const float m_new = fmaxf(m, dot), corr = expf(m - m_new), w = expf(dot - m_new);
+        l = l * corr + w;
+#pragma unroll
+        for (int i = 0; i < NR; i++) acc[i] = fmaf(w, cv[i], acc[i] * corr);
+        m = m_new;
+    }
+    float* part = la_sm + (size_t)warp * R;
+    float* ml = la_sm + (size_t)4 * R;
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+        const int r = lane + 32 * i;
+        if (r < R) part[r] = acc[i];
+    }
+    if (lane == 0) {
+        ml[2 * warp] = m;
+        ml[2 * warp + 1] = l;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w = 0; w < 4; w++) M = fmaxf(M, ml[2 * w]);
+    float f[4], L = 0.f;
+    for (int w = 0; w < 4; w++) {
+        f[w] = ml[2 * w + 1] > 0.f ? expf(ml[2 * w] - M) : 0.f;
+        L += ml[2 * w + 1] * f[w];
+    }
+    for (int r = threadIdx.x; r < R; r += 128) {
+        float v = 0.f;
+        for (int w = 0; w < 4; w++) v = fmaf(la_sm[(size_t)w * R + r], f[w], v);
+        out[((size_t)t * H + h) * R + r] = from_f32<TA>(v / L);
+    }
+}
+
+extern "C" int illm_latent_attention_any(const void* q, const void* kc, const int* block_table, int max_pages, const int* token_pos,
+                                         const int* token_seq, void* out, int act_dtype, int T, int H, int R, int page_size, int window,
+                                         float scale, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || H > 65535 || R <= 0 || R > 1024 || page_size <= 0 || window < 0) return ILLM_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = ((size_t)4 * R + 8) * sizeof(float);
+    const int nr = (R + 31) / 32;
+#define ILLM_LA(TA, NR)                                                                                                               \
+    illm_launch(latent_attention_any_kernel<TA, NR>, dim3(T, H), dim3(128), smem, s, (const TA*)q, (const TA*)kc, block_table, max_pages, \
+                token_pos, token_seq, (TA*)out, H, R, page_size, window, scale)
+#define ILLM_LA_NR(TA)                                  \
+    do {                                                \
+        if (nr <= 1) ILLM_LA(TA, 1);                    \
+        else if (nr <= 2) ILLM_LA(TA, 2);               \
+        else if (nr <= 4) ILLM_LA(TA, 4);               \
+        else if (nr <= 8) ILLM_LA(TA, 8);               \
+        else if (nr <= 16) ILLM_LA(TA, 16);             \
+        else ILLM_LA(TA, 32);                           \
+    } while (0)
+    if (act_dtype == ILLM_BF16) ILLM_LA_NR(bf16);
+    else if (act_dtype == ILLM_F32) ILLM_LA_NR(float);
+    else return ILLM_ERR_BAD_ARG;
+#undef ILLM_LA_NR
+#undef ILLM_LA
+    return illm_launch_status();
+}

@@ -730,6 +730,18 @@ Mat latent_prep(Device& dev, const Mat& x, int q_rank, int kv_rank, const float*
     return cq;
 }
 
+Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale) {
+    need(q, "q");
+    if (!kv.k || kv.n_kv_heads != 1 || kv.dtype != q.dtype || q.cols != (long long)heads * kv.head_dim)
+        throw KernelError("latent_attention_any: the queries and the cache entry (one head, the queries' dtype) do not fit together");
+    Mat out = new_mat(dev, q.rows, q.cols, q.dtype);
+    const int rc = illm_latent_attention_any(q.p, kv.k, kv.block_table, kv.width, ctx.token_pos, ctx.token_seq, out.p, code_of(q.dtype, "latent_attention_any"),
+                                             (int)q.rows, heads, kv.head_dim, kv.page_size, kv.window, scale, dev.stream());
+    if (rc == 10001) throw KernelError("latent_attention_any: a latent of " + std::to_string(kv.head_dim) + " channels is beyond the kernel (up to 1024)");
+    check_kernel(rc, "latent_attention_any");
+    return out;
+}
+
 Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype) {
     need(x, "x");
     need(w, "w");

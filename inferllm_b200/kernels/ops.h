@@ -257,6 +257,9 @@ Mat delta_rule(Device& dev, const Mat& x_f32, const Mat& a_f32, const DeltaRule&
 // query latent [T, q_rank] in `act_dtype`.  kv: a keys-only entry of one head of kv_rank channels.
 Mat latent_prep(Device& dev, const Mat& x_f32, int q_rank, int kv_rank, const float* w_q, const float* w_kv, float eps, const StepView& ctx,
                 const KVView& kv, DType act_dtype);
+// Attention of `heads` query heads over one shared key/value head of ANY width (a keys-only cache entry), float32 math:
+// for widths the framework's attention kernels do not take.  q [T, heads * width] in the cache's dtype.
+Mat latent_attention_any(Device& dev, const Mat& q, const KVView& kv, const StepView& ctx, int heads, float scale);
 // y[t, h, :] = W_h x[t, h, :] (transposed = false, w [heads * n_out, n_in]) or W_h^T x[t, h, :] (w [heads * n_in, n_out])
 Mat head_linear(Device& dev, const Mat& x, const Mat& w, int heads, bool transposed, DType out_dtype);
 

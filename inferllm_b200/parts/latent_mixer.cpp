@@ -39,9 +39,7 @@ struct LatentAttention : Mixer {
                  {"kv_norm", "kv_a_norm.weight"}, {"k_up", "k_b_proj.weight"}, {"v_up", "v_b_proj.weight"}, {"o", "o_proj.weight"}};
         if (s.has("names"))
             for (auto& m : s.params.at("names").members()) names[m.first] = m.second.as_string();
-        if (rt && (kv_rank % 8 || kv_rank > ops::kMaxHeadDimGeneric))
-            throw ConfigError("latent_attention: a latent of " + std::to_string(kv_rank) + " channels is not supported by the attention kernels (multiples of 8 up to " +
-                              std::to_string(ops::kMaxHeadDimGeneric) + ")");
+        if (rt && kv_rank > 1024) throw ConfigError("latent_attention: a latent of " + std::to_string(kv_rank) + " channels is beyond the kernels (up to 1024)");
     }
     bool graph_safe() const override { return true; }
     bool pad_safe() const override { return false; }
@@ -83,7 +81,9 @@ struct LatentAttention : Mixer {
         const ops::Geometry g{n_heads, 1, kv_rank};
         ops::AttentionExtras ex;
         ex.wide_weights = true;       // the softmax weights are not to be rounded to eight bits
-        Mat o = ops::attention_ex(dev, qa, kv, ctx, g, scale, ex);
+        // a latent whose width the framework's attention kernels do not take (not a multiple of 8, beyond 256) has a plain kernel
+        Mat o = (kv_rank % 8 || kv_rank > ops::kMaxHeadDimGeneric) ? ops::latent_attention_any(dev, qa, kv, ctx, n_heads, scale)
+                                                                  : ops::attention_ex(dev, qa, kv, ctx, g, scale, ex);
         Mat ov = ops::head_linear(dev, o, w_uv.m, n_heads, false, rt->dtype);         // U_v,h (sum p c)
         return ops::linear(dev, rt->gemm, ov, w_o.m, out_f32 ? DType::F32 : rt->dtype, may_defer);
     }

@@ -137,6 +137,8 @@ ALONE = {
     "latent_window": pz.random_config((L,), mlps=[None], bigram=None, window=5, scale=2.0),
     "dense": pz.random_config((L,), mlps=["dense"], bigram=None),
     "moe": pz.random_config((L,), mlps=["moe"], bigram=None, experts=7, top=3),
+    "latent_odd_width": pz.random_config((L,), mlps=[None], bigram=None, window=9, scale=1.5, kv_rank=21, q_rank=7, att_heads=3),
+    "latent_wide": pz.random_config((L,), mlps=[None], bigram=None, window=0, scale=0.4, kv_rank=264, att_heads=2),
     "bigram": pz.random_config((L,), mlps=[None], bigram=(17, 1000003, 999983)),
     "loop": pz.random_config((L, L), mlps=[None, None], bigram=None, loop=(0, 1, 3)),
 }
