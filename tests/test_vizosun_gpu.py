@@ -112,6 +112,10 @@ CONFIGS = {
     "odd": pz.random_config((D, L, D), width=56, vocab=75, heads=3, kv_heads=1, dim=20, vdim=12, conv=2, a_rank=3, g_rank=5, att_heads=7,
                             att_dim=12, att_vdim=20, q_rank=12, kv_rank=40, window=33, scale=0.8, experts=4, top=4, expert_ff=12, ff=44,
                             mlps=["moe", "dense", "moe"], loop=(0, 3, 2), bigram=(7, 3, 1)),
+    # an odd width and an odd vocabulary: no row of an activation or a matrix is a whole number of 16-byte pieces
+    "odd_width": pz.random_config((D, L, L), width=45, vocab=71, heads=3, kv_heads=3, dim=10, vdim=6, conv=3, a_rank=2, g_rank=2, att_heads=3,
+                                  att_dim=6, att_vdim=10, q_rank=9, kv_rank=24, window=11, scale=0.9, experts=3, top=2, expert_ff=10, ff=30,
+                                  mlps=["moe", "dense", None], loop=(1, 2, 2), bigram=(13, 5, 3)),
 }
 
 
